@@ -34,11 +34,16 @@ from .allocator import OutOfPages, PageAllocator, pages_for
 
 @dataclass(frozen=True)
 class PagedKVSpec:
-    """Keys and values of `num_kv_heads` heads of `head_dim`; `window` keys are kept
-    (None: all of them)."""
+    """Keys and values of `num_kv_heads` heads; keys have `head_dim` dims, values
+    `v_head_dim` (None: the same); `window` keys are kept (None: all of them)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -50,9 +55,18 @@ class StateSpec:
 
 @dataclass(frozen=True)
 class CacheNeeds:
-    """What one run of a layer asks of the cache manager."""
+    """What one run of a layer asks of the cache manager.  `state` is one StateSpec, or a
+    mapping name -> StateSpec for a mixer that keeps several tensors per request."""
     paged: Optional[PagedKVSpec] = None
-    state: Optional[StateSpec] = None
+    state: Optional[object] = None
+
+    def state_specs(self) -> Dict[str, StateSpec]:
+        """The state tensors by name ("" for a single unnamed one)."""
+        if self.state is None:
+            return {}
+        if isinstance(self.state, StateSpec):
+            return {"": self.state}
+        return dict(self.state)
 
 
 class PageGroup:
@@ -66,7 +80,7 @@ class PageGroup:
         self.allocator = PageAllocator(num_pages)
         shape = (len(entries), num_pages + 1, spec.num_kv_heads, page_size, spec.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros((*shape[:-1], spec.value_dim), dtype=dtype, device=device)
         self.table = torch.zeros((max_rows, table_width), dtype=torch.int32, device=device)
         self.host_table = torch.zeros((max_rows, table_width), dtype=torch.int32)
         # Logical block -> page for each row; 0 where nothing is held (never written,
@@ -109,11 +123,13 @@ class CacheManager:
         self.group_of_entry: Dict[int, int] = {
             e: gi for gi, g in enumerate(self.groups) for e in g.entries}
 
-        self.states: Dict[int, torch.Tensor] = {}
+        # entry -> {name: [max_rows, *shape]}; a single unnamed state has the name ""
+        self.states: Dict[int, Dict[str, torch.Tensor]] = {}
         for i, n in enumerate(needs):
-            if n is not None and n.state is not None:
-                self.states[i] = torch.zeros((max_rows, *n.state.shape), dtype=n.state.dtype,
-                                             device=self.device)
+            specs = n.state_specs() if n is not None else {}
+            if specs:
+                self.states[i] = {name: torch.zeros((max_rows, *s.shape), dtype=s.dtype, device=self.device)
+                                  for name, s in specs.items()}
         self._staging: List[Tuple[torch.Tensor, Optional[torch.cuda.Event]]] = []
         self._staging_next = 0
 
@@ -122,7 +138,7 @@ class CacheManager:
         """Device bytes that one more page per group costs (keys and values of every layer run
         of every group), for sizing the pool from a memory budget."""
         item = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * n.paged.num_kv_heads * page_size * n.paged.head_dim * item
+        return sum(n.paged.num_kv_heads * page_size * (n.paged.head_dim + n.paged.value_dim) * item
                    for n in needs if n is not None and n.paged is not None)
 
     # ------------------------------------------------------------------ views for mixers
@@ -139,9 +155,12 @@ class CacheManager:
     def window(self, entry: int) -> Optional[int]:
         return self.groups[self.group_of_entry[entry]].spec.window
 
-    def state(self, entry: int) -> torch.Tensor:
-        """State slots `[max_rows, *shape]` of one order entry."""
-        return self.states[entry]
+    def state(self, entry: int, name: str = "") -> torch.Tensor:
+        """State slots `[max_rows, *shape]` of one order entry (`name`: which, if it keeps several)."""
+        return self.states[entry][name]
+
+    def _state_tensors(self):
+        return [t for d in self.states.values() for t in d.values()]
 
     # ------------------------------------------------------------------ rows
     def assign(self, row: int) -> None:
@@ -150,7 +169,7 @@ class CacheManager:
             raise ValueError(f"row {row} is still in use")
         self.active[row] = True
         self.lengths[row] = 0
-        for t in self.states.values():
+        for t in self._state_tensors():
             t[row].zero_()
 
     def pages_needed(self, row: int, new_len: int) -> List[int]:
@@ -251,7 +270,7 @@ class CacheManager:
             g.host_table[dst].copy_(g.host_table[src])
             g.host_table[src].zero_()
             g.dirty.update((src, dst))
-        for t in self.states.values():
+        for t in self._state_tensors():
             t[dst].copy_(t[src])
         self.lengths[dst], self.lengths[src] = self.lengths[src], 0
         self.active[dst], self.active[src] = True, False
@@ -297,7 +316,8 @@ class CacheManager:
 
     def bytes_per_token(self) -> int:
         item = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(g.entries) * g.spec.num_kv_heads * g.spec.head_dim * item for g in self.groups)
+        return sum(len(g.entries) * g.spec.num_kv_heads * (g.spec.head_dim + g.spec.value_dim) * item
+                   for g in self.groups)
 
     def check(self) -> None:
         """No page lost, held twice or freed twice; tables agree with ownership."""

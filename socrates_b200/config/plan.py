@@ -39,7 +39,7 @@ class LayerSpec:
     prefix: str
     norms: Tuple[PartSpec, ...]
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]      # None: the layer has a mixer only
 
 
 @dataclass(frozen=True)
@@ -49,11 +49,14 @@ class RunEntry:
     `layer` indexes `ModelPlan.layers` and may repeat: the same weights run twice,
     each run with a cache of its own.  `reads_cache_of` names an earlier entry (by
     its index in `ModelPlan.order`) whose cache this run reads instead of writing
-    one of its own.
+    one of its own.  `before` names a part of the group "stream_op" that acts on the
+    residual stream right before this run (something added at the start of a pass over
+    repeated layers, for instance); the parts' tensor names are relative to the model.
     """
 
     layer: int
     reads_cache_of: Optional[int] = None
+    before: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

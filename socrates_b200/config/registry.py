@@ -11,6 +11,7 @@ import json
 from pathlib import Path
 from typing import Any, Dict, Mapping
 
+from .bofusun import BofusunConfig
 from .qwen3 import ConfigError, Qwen3Config
 
 _ARCHITECTURES: Dict[str, Any] = {}
@@ -34,9 +35,9 @@ def known_architectures() -> list[str]:
 
 
 def config_from_dict(d: Mapping[str, Any]):
-    archs = d.get("architectures")
+    archs = d.get("architectures") or ([d["architecture"]] if d.get("architecture") else None)
     if not archs:
-        raise ConfigError("config.json has no 'architectures' entry; known: "
+        raise ConfigError("config.json has neither an 'architectures' list nor an 'architecture' name; known: "
                           + ", ".join(known_architectures()))
     name = archs[0]
     if name not in _ARCHITECTURES:
@@ -55,3 +56,4 @@ def load_config(model_dir: str | Path):
 
 
 register_architecture(Qwen3Config.architecture, Qwen3Config)
+register_architecture(BofusunConfig.architecture, BofusunConfig)

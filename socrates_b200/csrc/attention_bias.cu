@@ -1,0 +1,180 @@
+// Paged causal attention with capped scores, a bias by distance and a gate per head, on the
+// CUDA cores.  Every token of the step is a query of its own (prompt portions and decoded
+// tokens alike); the step's keys and values are already in the pages.
+//
+//   s_ij = (q_i . k_j) * scale
+//   s_ij = cap * tanh(s_ij / cap)                  (cap > 0)
+//   s_ij += dist_bias[h][min(i - j, L - 1)]        (a table by distance, made on the host)
+//   keys j with 0 <= i - j < window                (window 0: all keys)
+//   o_i = softmax_j(s_ij) v_j * sigmoid(gate_i[h]) (gate optional)
+//
+// Keys have `Dk` dims and values `Dv`; they may differ, and the two pools are shaped accordingly.
+// Scores, softmax weights and the weighted sum are float32.  One block serves the query heads of
+// one KV head for one token, running over the visible keys in chunks with a running maximum.
+#include <math.h>
+
+#include "common.cuh"
+
+using namespace sb;
+
+namespace {
+
+constexpr int THREADS = 128;
+constexpr int KEYS = 128;      // keys per chunk: one per thread
+constexpr int HEADS = 4;       // query heads per pass over the keys
+constexpr int DMAX = 256;
+
+struct BiasAttnArgs {
+    void* out;                 // [N, Hq*Dv] in T
+    const void* q;             // [N, Hq*Dk] in T
+    const void* k_pool;        // [pages, Hkv, BS, Dk] in T
+    const void* v_pool;        // [pages, Hkv, BS, Dv] in T
+    const int* block_table;
+    int table_width;
+    const int* token_rows;
+    const int* positions;
+    const void* gate;          // [N, gate_stride] in T, head h at column h; or null
+    long long gate_stride;
+    const float* dist_bias;    // [Hq, L] or null
+    int L;
+    int Hq, Hkv, Dk, Dv, BS, window;
+    float scale, cap;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS) bias_attention_kernel(BiasAttnArgs a) {
+    sb::pdl_launch_dependents();
+    sb::pdl_wait();
+    __shared__ float qs[HEADS][DMAX];
+    __shared__ float w[HEADS][KEYS];
+    __shared__ float run_max[HEADS], run_sum[HEADS], rescale[HEADS];
+    const int kh = blockIdx.x, n = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = a.Hq / a.Hkv, Dk = a.Dk, Dv = a.Dv, BS = a.BS;
+    const int row = a.token_rows[n], pos = a.positions[n];
+    const int lo = (a.window > 0 && pos + 1 > a.window) ? pos + 1 - a.window : 0;
+    const int* table = a.block_table + (size_t)row * a.table_width;
+    const T* q = (const T*)a.q;
+    const T* kp = (const T*)a.k_pool;
+    const T* vp = (const T*)a.v_pool;
+
+    for (int g0 = 0; g0 < G; g0 += HEADS) {
+        const int gn = min(HEADS, G - g0), h0 = kh * G + g0;
+        __syncthreads();
+        for (int i = tid; i < gn * Dk; i += THREADS) {
+            const int g = i / Dk, d = i - g * Dk;
+            qs[g][d] = to_float(q[((size_t)n * a.Hq + h0 + g) * Dk + d]);
+        }
+        if (tid < HEADS) { run_max[tid] = -INFINITY; run_sum[tid] = 0.f; rescale[tid] = 0.f; }
+        float acc[HEADS][2];
+#pragma unroll
+        for (int g = 0; g < HEADS; ++g) acc[g][0] = acc[g][1] = 0.f;
+        __syncthreads();
+        for (int c0 = lo; c0 <= pos; c0 += KEYS) {
+            const int nk = min(KEYS, pos + 1 - c0);
+            // scores of one key per thread, for all heads of the pass
+            if (tid < nk) {
+                const int key = c0 + tid;
+                const T* kr = kp + (((size_t)table[key / BS] * a.Hkv + kh) * BS + key % BS) * Dk;
+                float dot[HEADS];
+#pragma unroll
+                for (int g = 0; g < HEADS; ++g) dot[g] = 0.f;
+                for (int d = 0; d < Dk; ++d) {
+                    const float kf = to_float(kr[d]);
+#pragma unroll
+                    for (int g = 0; g < HEADS; ++g) dot[g] = fmaf(qs[g][d], kf, dot[g]);
+                }
+                const int dist = min(pos - key, a.L - 1);
+#pragma unroll
+                for (int g = 0; g < HEADS; ++g) {
+                    if (g >= gn) continue;
+                    float s = dot[g] * a.scale;
+                    if (a.cap > 0.f) s = a.cap * tanhf(s / a.cap);
+                    if (a.dist_bias) s += a.dist_bias[(size_t)(h0 + g) * a.L + dist];
+                    w[g][tid] = s;
+                }
+            }
+            __syncthreads();
+            // running maximum and weights, one warp per head
+            for (int g = warp; g < gn; g += THREADS / 32) {
+                float mx = -INFINITY;
+                for (int t = lane; t < nk; t += 32) mx = fmaxf(mx, w[g][t]);
+                mx = warp_max(mx);
+                const float m_old = run_max[g], m_new = fmaxf(m_old, mx);
+                float sum = 0.f;
+                for (int t = lane; t < nk; t += 32) {
+                    const float p = expf(w[g][t] - m_new);
+                    w[g][t] = p;
+                    sum += p;
+                }
+                sum = warp_sum(sum);
+                if (lane == 0) {
+                    const float f = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+                    rescale[g] = f;
+                    run_sum[g] = run_sum[g] * f + sum;
+                    run_max[g] = m_new;
+                }
+            }
+            __syncthreads();
+            // weighted sum of the values: thread t owns dims t and t + THREADS
+#pragma unroll
+            for (int g = 0; g < HEADS; ++g) { acc[g][0] *= rescale[g]; acc[g][1] *= rescale[g]; }
+            for (int t = 0; t < nk; ++t) {
+                const int key = c0 + t;
+                const T* vr = vp + (((size_t)table[key / BS] * a.Hkv + kh) * BS + key % BS) * Dv;
+                const float v0 = tid < Dv ? to_float(vr[tid]) : 0.f;
+                const float v1 = tid + THREADS < Dv ? to_float(vr[tid + THREADS]) : 0.f;
+#pragma unroll
+                for (int g = 0; g < HEADS; ++g) {
+                    if (g >= gn) continue;
+                    acc[g][0] = fmaf(w[g][t], v0, acc[g][0]);
+                    acc[g][1] = fmaf(w[g][t], v1, acc[g][1]);
+                }
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int g = 0; g < HEADS; ++g) {
+            if (g >= gn) continue;
+            const int h = h0 + g;
+            float f = 1.0f / run_sum[g];
+            if (a.gate) {
+                const float z = to_float(((const T*)a.gate)[(size_t)n * a.gate_stride + h]);
+                f *= 1.0f / (1.0f + expf(-z));
+            }
+            T* o = (T*)a.out + ((size_t)n * a.Hq + h) * Dv;
+            if (tid < Dv) o[tid] = from_float<T>(acc[g][0] * f);
+            if (tid + THREADS < Dv) o[tid + THREADS] = from_float<T>(acc[g][1] * f);
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" int sb_attention_bias(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                 const int* block_table, int table_width, const int* token_rows,
+                                 const int* positions, const void* gate, long long gate_stride,
+                                 const float* dist_bias, int L, int N, int Hq, int Hkv, int Dk, int Dv,
+                                 int page_size, int window, float scale, float cap, int dtype,
+                                 cudaStream_t stream) {
+    SB_REQUIRE(N >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0,
+               "attention_bias: %d query heads are no multiple of %d KV heads", Hq, Hkv);
+    SB_REQUIRE(Dk >= 1 && Dk <= DMAX && Dv >= 1 && Dv <= 2 * THREADS,
+               "attention_bias: head sizes %d (keys) and %d (values) must be at most %d", Dk, Dv, DMAX);
+    SB_REQUIRE(page_size > 0 && table_width > 0, "attention_bias: bad page_size %d or table width %d", page_size,
+               table_width);
+    SB_REQUIRE(window >= 0, "attention_bias: window %d is negative", window);
+    SB_REQUIRE(dist_bias == nullptr || L >= 1, "attention_bias: a bias table needs a length");
+    SB_REQUIRE(N <= 65535, "attention_bias: %d tokens exceed one launch", N);
+    if (N == 0) return 0;
+    BiasAttnArgs a;
+    a.out = out; a.q = q; a.k_pool = k_pool; a.v_pool = v_pool; a.block_table = block_table;
+    a.table_width = table_width; a.token_rows = token_rows; a.positions = positions; a.gate = gate;
+    a.gate_stride = gate_stride; a.dist_bias = dist_bias; a.L = L > 0 ? L : 1; a.Hq = Hq; a.Hkv = Hkv; a.Dk = Dk;
+    a.Dv = Dv; a.BS = page_size; a.window = window; a.scale = scale; a.cap = cap;
+    dim3 grid(Hkv, N);
+    if (dtype == SB_F32) sb::launch(bias_attention_kernel<float>, grid, dim3(THREADS), 0, stream, a);
+    else if (dtype == SB_BF16) sb::launch(bias_attention_kernel<__nv_bfloat16>, grid, dim3(THREADS), 0, stream, a);
+    else SB_REQUIRE(false, "attention_bias: unknown dtype %d", dtype);
+    SB_LAUNCH_CHECK();
+}

@@ -89,6 +89,7 @@ class CacheView:
         self.manager = manager
         self.entry = entry          # the order entry whose pools and state are used
         self.writes = writes        # False: this run reads another run's cache
+        self.prefix = ""            # in front of state names (see sub)
 
     def pools(self):
         return self.manager.pools(self.entry)
@@ -96,8 +97,14 @@ class CacheView:
     def block_table(self) -> torch.Tensor:
         return self.manager.block_table(self.entry)
 
-    def state(self) -> torch.Tensor:
-        return self.manager.state(self.entry)
+    def state(self, name: str = "") -> torch.Tensor:
+        return self.manager.state(self.entry, self.prefix + name)
+
+    def sub(self, prefix: str) -> "CacheView":
+        """The same cache for a part inside a mixer: its state names get `prefix` in front."""
+        view = CacheView(self.manager, self.entry, self.writes)
+        view.prefix = self.prefix + prefix
+        return view
 
 
 class StepContext:
@@ -118,6 +125,7 @@ class StepContext:
         self.token_feedback = token_feedback   # int32 device tokens that ids -1 - j stand for (see ops.embed)
         self.weight_successor: Dict[int, torch.Tensor] = {}   # set by the model: address -> next weights
         self.l2_prefetch_bytes = _l2_prefetch_budget()
+        self.after_run = None               # callable(order index, stream) after every layer run (for inspection)
 
     # ------------------------------------------------------------------ kernel choice
     def uses_tensor_cores(self, x_dtype: torch.dtype, w: torch.Tensor) -> bool:

@@ -30,6 +30,11 @@ class Model:
             if spec.arrangement not in reg:
                 raise KeyError(f"no arrangement {spec.arrangement!r}; known: {sorted(reg)}")
             self.layers.append(reg[spec.arrangement](spec))
+        # parts that act on the stream right before a run (RunEntry.before), by order index
+        self.stream_ops = {i: build_part("stream_op", e.before, e.before.name)
+                           for i, e in enumerate(plan.order) if e.before is not None}
+        self.keeps_embedding_output = any(getattr(op, "needs_embedding_output", False)
+                                          for op in self.stream_ops.values())
         self.final_norm = build_part("norm", plan.final_norm, plan.final_norm.name)
         self.head = build_part("head", plan.head, plan.head.name)
         self.dtype: Optional[torch.dtype] = None
@@ -37,7 +42,7 @@ class Model:
     # ------------------------------------------------------------------ weights
     def parameters(self) -> Dict[str, ParamSpec]:
         out: Dict[str, ParamSpec] = {}
-        for part in (self.embedding, *self.layers, self.final_norm, self.head):
+        for part in (self.embedding, *self.layers, *self.stream_ops.values(), self.final_norm, self.head):
             for name, spec in part.parameters().items():
                 if name in out and out[name].shape != spec.shape:
                     raise ValueError(f"{name} is asked for with shapes {out[name].shape} and {spec.shape}")
@@ -54,7 +59,7 @@ class Model:
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype) -> None:
         self.dtype = dtype
-        for part in (self.embedding, *self.layers, self.final_norm, self.head):
+        for part in (self.embedding, *self.layers, *self.stream_ops.values(), self.final_norm, self.head):
             part.bind(tensors, dtype)
         # The weight matrices in the order in which a step streams them (parts that say so
         # through streamed_weights()), as a map from each one's address to its successor: a
@@ -77,16 +82,28 @@ class Model:
 
     @property
     def supports_graph(self) -> bool:
-        return all(l.supports_graph for l in self.layers)
+        return (all(l.supports_graph for l in self.layers)
+                and all(getattr(op, "supports_graph", True) for op in self.stream_ops.values()))
 
     # ------------------------------------------------------------------ one step
     def forward(self, ctx: StepContext, cache) -> torch.Tensor:
         ctx.weight_successor = self.weight_successor
         stream = ResidualStream(self.embedding.forward(ctx))
+        if self.keeps_embedding_output:
+            # the residual is updated in place from here on: a stream op that adds the embedding's
+            # output again later reads this copy
+            keep = ctx.buffers.take("embedding_output", ctx.num_tokens, (self.plan.hidden_size,), torch.float32)
+            keep.copy_(stream.residual)
+            stream.embedding_output = keep
         for i, e in enumerate(self.plan.order):
+            op = self.stream_ops.get(i)
+            if op is not None:
+                op.apply(ctx, stream)
             src = e.reads_cache_of
             view = CacheView(cache, i if src is None else src, writes=src is None)
             self.layers[e.layer].forward(ctx, stream, view)
+            if ctx.after_run is not None:
+                ctx.after_run(i, stream)
         if ctx.logit_index is None:
             return None          # no logits wanted: the last branch is never needed
         h = self.final_norm.apply(ctx, stream, row_index=ctx.logit_index, buffer="normed_out")

@@ -47,6 +47,14 @@ _SIGNATURES = {
     "sb_attention_decode_stream": [P, P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, I, P],
     "sb_attention_tcgen05_supports": [I, I, I, I],
     "sb_attention_prefill_tcgen05": [P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P],
+    "sb_fold_rmsnorm": [P, P, I, LL, P, P, F, P, P, P, P, P, I, I, F, I, P],
+    "sb_normed_mean": [P, P, I, LL, P, P, I, LL, P, I, I, F, F, P],
+    "sb_bias_act": [P, P, P, I, LL, P, I, I, I, I, P],
+    "sb_short_conv": [P, LL, P, P, P, I, P, I, I, I, P, P, P, I, I, I, P, P, P, P, P, P, P, I, P],
+    "sb_short_conv_tail": [P, P, LL, P, I, I, P, P, I, I, P],
+    "sb_retention": [P, LL, I, I, I, I, P, P, P, I, P, P, P, P, I, I, I, I, F, F, I, P],
+    "sb_selective_scan": [P, LL, P, LL, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, P],
+    "sb_attention_bias": [P, P, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, I, I, F, F, I, P],
 }
 
 

@@ -464,3 +464,250 @@ def attention_prefill_tcgen05(out: torch.Tensor, q: torch.Tensor, k_pool: torch.
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), pages, _ptr(block_table), block_table.shape[1],
         _ptr(seq_starts), _ptr(seq_rows), _ptr(seq_first_pos), R, N, num_heads, Hkv, D, BS, int(window),
         float(scale), _ptr(status), _stream()), "attention_prefill_tcgen05")
+
+
+# ---------------------------------------------------------------------------------------------
+# Kernels of blocks that norm a branch before it joins the residual, and of recurrent mixers.
+
+ACTIVATIONS = {"identity": 0, "relu_squared": 1, "gelu_tanh": 2, "silu": 3}
+
+
+def fold_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: Optional[torch.Tensor],
+                 out: Optional[torch.Tensor], eps: float, row_index: Optional[torch.Tensor] = None,
+                 branch_bias: Optional[torch.Tensor] = None, branch_gain: Optional[torch.Tensor] = None,
+                 branch_eps: float = 0.0, add_rows: Optional[torch.Tensor] = None,
+                 add_vec: Optional[torch.Tensor] = None) -> None:
+    """b = sum(delta, 0) + branch_bias; with `branch_gain` b = b / sqrt(mean(b^2) + branch_eps) * branch_gain;
+    residual += b + add_rows + add_vec; out = residual / sqrt(mean(residual^2) + eps) * gain.
+
+    residual float32 [N, d]; delta float32 [S, N, d] or None; the gains, the bias and add_vec float32 [d];
+    add_rows float32 [N, d]; out [M, d] in float32 or bfloat16, or None (only the residual moves on).  With
+    `row_index` only the named rows are computed and the residual is left as it is.
+    """
+    N, d = residual.shape
+    _want(residual, "residual", torch.float32)
+    S, stride = 0, 0
+    if delta is not None:
+        _want(delta, "delta", torch.float32)
+        if delta.dim() != 3 or delta.shape[1:] != (N, d):
+            raise KernelError(f"delta must be [S, {N}, {d}], got {tuple(delta.shape)}")
+        S, stride = delta.shape[0], N * d
+    for t, nm in ((gain, "gain"), (branch_bias, "branch_bias"), (branch_gain, "branch_gain"), (add_vec, "add_vec")):
+        if t is not None:
+            _want(t, nm, torch.float32, (d,))
+    if add_rows is not None:
+        _want(add_rows, "add_rows", torch.float32, (N, d))
+    M = N
+    if row_index is not None:
+        _want(row_index, "row_index", torch.int32)
+        M = row_index.numel()
+    code = 0
+    if out is not None:
+        _want(out, "out", None, (M, d))
+        code = _code(out.dtype)
+    lib = library()
+    check(lib, lib.sb_fold_rmsnorm(_ptr(residual), _ptr(delta), S, stride, _ptr(branch_bias), _ptr(branch_gain),
+                                   float(branch_eps), _ptr(add_rows), _ptr(add_vec), _ptr(gain), _ptr(out),
+                                   _ptr(row_index), M, d, float(eps), code, _stream()), "fold_rmsnorm")
+
+
+def normed_mean(out: torch.Tensor, x0: torch.Tensor, gain0: torch.Tensor, x1: torch.Tensor, gain1: torch.Tensor,
+                eps: float, scale: float = 0.5) -> None:
+    """out = scale * (unit_rms(sum(x0, 0)) * gain0 + unit_rms(sum(x1, 0)) * gain1); x float32 [S, N, d]
+    partial sums, out float32 [N, d]."""
+    N, d = out.shape
+    _want(out, "out", torch.float32)
+    for x, g in ((x0, gain0), (x1, gain1)):
+        _want(x, "x", torch.float32)
+        if x.dim() != 3 or x.shape[1:] != (N, d):
+            raise KernelError(f"a term must be [S, {N}, {d}], got {tuple(x.shape)}")
+        _want(g, "gain", torch.float32, (d,))
+    lib = library()
+    check(lib, lib.sb_normed_mean(_ptr(out), _ptr(x0), x0.shape[0], N * d, _ptr(gain0), _ptr(x1), x1.shape[0],
+                                  N * d, _ptr(gain1), N, d, float(eps), float(scale), _stream()), "normed_mean")
+
+
+def bias_act(out: torch.Tensor, x: torch.Tensor, bias: Optional[torch.Tensor], activation: str) -> None:
+    """out = act(x + bias); x [N, F] in out's dtype, or float32 partial sums [S, N, F] that are added first."""
+    N, F_ = out.shape
+    _want(out, "out")
+    parts = x.dim() == 3
+    if parts:
+        _want(x, "x partial sums", torch.float32, (x.shape[0], N, F_))
+    else:
+        _want(x, "x", out.dtype, (N, F_))
+    if bias is not None:
+        _want(bias, "bias", torch.float32, (F_,))
+    lib = library()
+    check(lib, lib.sb_bias_act(_ptr(out), None if parts else _ptr(x), _ptr(x) if parts else None,
+                               x.shape[0] if parts else 0, N * F_, _ptr(bias), N, F_, ACTIVATIONS[activation],
+                               _code(out.dtype), _stream()), "bias_act")
+
+
+def short_conv(x: torch.Tensor, in_bias: Optional[torch.Tensor], taps: torch.Tensor,
+               conv_bias: Optional[torch.Tensor], silu: bool, tail: Optional[torch.Tensor],
+               token_rows: torch.Tensor, positions: torch.Tensor, destinations,
+               block_table: Optional[torch.Tensor] = None) -> None:
+    """Causal convolution over time of the first C columns of x [N, >= C], per channel.
+
+    y_t = act(sum_j taps[:, j] * (x + in_bias)_{t-K+1+j} + conv_bias), zeros before a sequence's start; tokens
+    before the step's portion come from `tail` float32 [rows, K-1, C] (not changed here: `short_conv_tail`).
+    `destinations`: up to three (begin, end, tensor) column ranges; a 2-d tensor [N, end-begin] is written
+    densely, a 4-d pool [pages, heads, page_size, head_dim] at each token's slot through `block_table`.
+    """
+    C, K = taps.shape
+    N = x.shape[0]
+    if x.dim() != 2 or x.shape[1] < C or x.stride(1) != 1:
+        raise KernelError(f"x must be [N, >= {C}] with unit column stride, got {tuple(x.shape)}")
+    if not x.is_cuda:
+        raise KernelError("x must be a CUDA tensor")
+    _want(taps, "taps", torch.float32)
+    for t, nm in ((in_bias, "in_bias"), (conv_bias, "conv_bias")):
+        if t is not None:
+            _want(t, nm, torch.float32, (C,))
+    if K > 1:
+        _want(tail, "tail", torch.float32)
+        if tail.shape[1:] != (K - 1, C):
+            raise KernelError(f"tail must be [rows, {K - 1}, {C}], got {tuple(tail.shape)}")
+    _want(token_rows, "token_rows", torch.int32, (N,))
+    _want(positions, "positions", torch.int32, (N,))
+    n = len(destinations)
+    if not 1 <= n <= 3:
+        raise KernelError("short_conv takes one to three destinations")
+    IntArr, PtrArr, LLArr = ctypes.c_int * n, ctypes.c_void_p * n, ctypes.c_longlong * n
+    begin, end, paged, dst, stride, heads, hd = IntArr(), IntArr(), IntArr(), PtrArr(), LLArr(), IntArr(), IntArr()
+    page_size = 0
+    for i, (b, e, t) in enumerate(destinations):
+        _want(t, "destination", x.dtype)
+        begin[i], end[i], dst[i] = b, e, t.data_ptr()
+        if t.dim() == 2:
+            if t.shape != (N, e - b):
+                raise KernelError(f"a dense destination must be [{N}, {e - b}], got {tuple(t.shape)}")
+            paged[i], stride[i], heads[i], hd[i] = 0, e - b, 0, 0
+        elif t.dim() == 4:
+            if t.shape[1] * t.shape[3] != e - b:
+                raise KernelError(f"a pool of {t.shape[1]} x {t.shape[3]} does not hold {e - b} channels")
+            paged[i], stride[i], heads[i], hd[i] = 1, 0, t.shape[1], t.shape[3]
+            page_size = t.shape[2]
+            if block_table is None:
+                raise KernelError("a paged destination needs the block table")
+        else:
+            raise KernelError("a destination is a matrix or a pool")
+    if block_table is not None:
+        _want(block_table, "block_table", torch.int32)
+    lib = library()
+    check(lib, lib.sb_short_conv(_ptr(x), x.stride(0), _ptr(in_bias), _ptr(taps), _ptr(conv_bias), int(silu),
+                                 _ptr(tail), C, K, N, _ptr(token_rows), _ptr(positions), _ptr(block_table),
+                                 block_table.shape[1] if block_table is not None else 0, page_size, n, begin, end,
+                                 paged, dst, stride, heads, hd, _code(x.dtype), _stream()), "short_conv")
+
+
+def short_conv_tail(tail: torch.Tensor, x: torch.Tensor, in_bias: Optional[torch.Tensor], taps: int,
+                    seq_starts: torch.Tensor, seq_rows: torch.Tensor) -> None:
+    """Move every request's tail on: it becomes the last K-1 values of (old tail, the step's x + in_bias)."""
+    if taps <= 1:
+        return
+    R = seq_rows.numel()
+    C = tail.shape[2]
+    _want(tail, "tail", torch.float32)
+    if x.dim() != 2 or x.shape[1] < C or x.stride(1) != 1 or not x.is_cuda:
+        raise KernelError(f"x must be a CUDA matrix [N, >= {C}] with unit column stride")
+    _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
+    _want(seq_rows, "seq_rows", torch.int32, (R,))
+    lib = library()
+    check(lib, lib.sb_short_conv_tail(_ptr(tail), _ptr(x), x.stride(0), _ptr(in_bias), C, taps, _ptr(seq_starts),
+                                      _ptr(seq_rows), R, _code(x.dtype), _stream()), "short_conv_tail")
+
+
+def retention(out: torch.Tensor, qkvg: torch.Tensor, offsets: Tuple[int, int, int, int], state: torch.Tensor,
+              decay: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, seq_starts: torch.Tensor,
+              seq_rows: torch.Tensor, seq_first_pos: torch.Tensor, eps: float, k_scale: float) -> None:
+    """Decayed linear attention of every request's tokens of the step, in order, through its state slot.
+
+    qkvg [N, width] holds q, k (H x dk each), v and g (H x dv each) at the column `offsets`; state float32
+    [rows, H, dk, dv] is read and left advanced; out [N, H*dv] = unit_rms(S^T q) * silu(g) per head."""
+    N = qkvg.shape[0]
+    _, H, dk, dv = state.shape
+    R = seq_rows.numel()
+    _want(qkvg, "qkvg", out.dtype)
+    _want(out, "out", None, (N, H * dv))
+    _want(state, "state", torch.float32)
+    _want(decay, "decay", torch.float32, (H,))
+    _want(inv_freq, "inv_freq", torch.float32)
+    if inv_freq.numel() < rotary_dim // 2:
+        raise KernelError(f"inv_freq has {inv_freq.numel()} entries for rotary_dim {rotary_dim}")
+    _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
+    _want(seq_rows, "seq_rows", torch.int32, (R,))
+    _want(seq_first_pos, "seq_first_pos", torch.int32, (R,))
+    lib = library()
+    check(lib, lib.sb_retention(_ptr(qkvg), qkvg.stride(0), *[int(o) for o in offsets], _ptr(state), _ptr(decay),
+                                _ptr(inv_freq), int(rotary_dim), _ptr(out), _ptr(seq_starts), _ptr(seq_rows),
+                                _ptr(seq_first_pos), R, H, dk, dv, float(eps), float(k_scale), _code(out.dtype),
+                                _stream()), "retention")
+
+
+def selective_scan(out: torch.Tensor, x: torch.Tensor, z: torch.Tensor, dt_raw: torch.Tensor,
+                   dt_bias: torch.Tensor, bc: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor,
+                   state: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor) -> None:
+    """Selective scan of every request's tokens of the step, in order, through its state slot.
+
+    x, z [N, inner] (row strides may exceed inner), bc [N, 2*states] (B then C) in out's dtype; dt_raw float32
+    [N, inner] before bias and softplus; A_log float32 [inner, states]; state float32 [rows, inner, states]."""
+    N, inner = out.shape
+    states = A_log.shape[1]
+    R = seq_rows.numel()
+    _want(out, "out")
+    for t, nm, cols in ((x, "x", inner), (z, "z", inner), (bc, "bc", 2 * states)):
+        if t.dtype != out.dtype or t.dim() != 2 or t.shape[0] != N or t.shape[1] < cols or t.stride(1) != 1:
+            raise KernelError(f"{nm} must be [{N}, >= {cols}] in {out.dtype} with unit column stride")
+    _want(dt_raw, "dt_raw", torch.float32, (N, inner))
+    _want(dt_bias, "dt_bias", torch.float32, (inner,))
+    _want(A_log, "A_log", torch.float32, (inner, states))
+    _want(D, "D", torch.float32, (inner,))
+    _want(state, "state", torch.float32)
+    if state.shape[1:] != (inner, states):
+        raise KernelError(f"state must be [rows, {inner}, {states}], got {tuple(state.shape)}")
+    _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
+    _want(seq_rows, "seq_rows", torch.int32, (R,))
+    lib = library()
+    check(lib, lib.sb_selective_scan(_ptr(x), x.stride(0), _ptr(z), z.stride(0), _ptr(dt_raw), _ptr(dt_bias),
+                                     _ptr(bc), bc.stride(0), _ptr(A_log), _ptr(D), _ptr(state), _ptr(out),
+                                     _ptr(seq_starts), _ptr(seq_rows), R, inner, states, _code(out.dtype),
+                                     _stream()), "selective_scan")
+
+
+def attention_bias(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                   block_table: torch.Tensor, token_rows: torch.Tensor, positions: torch.Tensor, num_heads: int,
+                   scale: float, window: int = 0, softcap: float = 0.0,
+                   dist_bias: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
+    """Paged causal attention, one query per token, with scores capped by softcap * tanh(s / softcap)
+    (0: no cap), a float32 bias table [Hq, L] by distance (distances past L-1 use the last entry) and a
+    sigmoid gate per head (gate [N, >= Hq], head h at column h).  Keys and values may have different head
+    sizes: q [N, Hq*Dk], k_pool [pages, Hkv, BS, Dk], v_pool [pages, Hkv, BS, Dv], out [N, Hq*Dv]."""
+    N = q.shape[0]
+    pages, Hkv, BS, Dk = k_pool.shape
+    Dv = v_pool.shape[3]
+    Hq = num_heads
+    _want(q, "q", k_pool.dtype, (N, Hq * Dk))
+    _want(out, "out", q.dtype, (N, Hq * Dv))
+    _want(k_pool, "k_pool")
+    _want(v_pool, "v_pool", k_pool.dtype, (pages, Hkv, BS, Dv))
+    _want(block_table, "block_table", torch.int32)
+    _want(token_rows, "token_rows", torch.int32, (N,))
+    _want(positions, "positions", torch.int32, (N,))
+    L = 0
+    if dist_bias is not None:
+        _want(dist_bias, "dist_bias", torch.float32)
+        if dist_bias.dim() != 2 or dist_bias.shape[0] != Hq:
+            raise KernelError(f"dist_bias must be [{Hq}, L], got {tuple(dist_bias.shape)}")
+        L = dist_bias.shape[1]
+    gate_stride = 0
+    if gate is not None:
+        if gate.dtype != q.dtype or gate.dim() != 2 or gate.shape[0] != N or gate.shape[1] < Hq or gate.stride(1) != 1:
+            raise KernelError(f"gate must be [{N}, >= {Hq}] in {q.dtype} with unit column stride")
+        gate_stride = gate.stride(0)
+    lib = library()
+    check(lib, lib.sb_attention_bias(_ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+                                     block_table.shape[1], _ptr(token_rows), _ptr(positions), _ptr(gate), gate_stride,
+                                     _ptr(dist_bias), L, N, Hq, Hkv, Dk, Dv, BS, int(window), float(scale),
+                                     float(softcap), _code(q.dtype), _stream()), "attention_bias")

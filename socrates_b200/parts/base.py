@@ -14,6 +14,9 @@ layer by the plan.  The five kinds and what each must provide:
 * **feed_forward**   `forward(ctx, x [N, d]) -> Branch`.
 * **arrangement**    `forward(ctx, stream, cache: CacheView)`: wires norms, mixer and
                      feed-forward of one layer around the residual stream.
+* **stream_op**      `apply(ctx, stream)`: acts on the residual stream between layer runs
+                     (named by `RunEntry.before`); `needs_embedding_output = True` makes the
+                     model keep the embedding's output on the stream for it.
 
 A `Branch` is the float32 output of a mixer or feed-forward as `S` partial sums
 `[S, N, d]` (S > 1 when the last matrix product was split along K); the next norm
@@ -38,12 +41,26 @@ class ParamSpec:
     """One tensor a part expects: its shape, and how random weights are drawn for it.
 
     role "matrix": a weight matrix, kept in the model dtype (bfloat16 or float32).
-    role "gain":   a norm gain, always held as float32 on the device.
-    init "normal": N(0, 0.02); init "gain": 1 + N(0, 0.1).
+    role "gain":   a norm gain (or another small float32 parameter), always held as float32 on the device.
+    role "int":    an integer table, int32 on the device.
+    init "normal": N(0, 0.02); init "gain": 1 + N(0, 0.1); init "around_zero": N(0, 0.1);
+    init "uniform": U(lo, hi) with `bounds` = (lo, hi).
     """
     shape: Tuple[int, ...]
     role: str = "matrix"
     init: str = "normal"
+    bounds: Tuple[float, float] = (0.0, 1.0)
+    # A dim of -1 in `shape` is read from the file (a table whose length the configuration does
+    # not give); `default_shape` is what random weights are drawn with then.
+    default_shape: Optional[Tuple[int, ...]] = None
+
+    def matches(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(a == -1 or a == b for a, b in zip(self.shape, shape))
+
+    @property
+    def draw_shape(self) -> Tuple[int, ...]:
+        return tuple(self.default_shape) if self.default_shape is not None else tuple(self.shape)
 
 
 class Part:
@@ -65,8 +82,20 @@ class Part:
 
 @dataclass
 class Branch:
-    """Float32 partial sums `[S, N, d]` waiting to be added to the residual."""
+    """Float32 partial sums `[S, N, d]` waiting to be added to the residual.
+
+    `bias` (float32 [d]) is added to their sum; with `post_gain` the sum is first normed
+    (x / sqrt(mean(x^2) + post_eps) * post_gain) and joins the residual only then: a block
+    that norms its branches on both sides sets these, and whoever folds the branch into the
+    residual (the next norm's kernel) does the arithmetic."""
     partial: torch.Tensor
+    bias: Optional[torch.Tensor] = None
+    post_gain: Optional[torch.Tensor] = None
+    post_eps: float = 0.0
+
+    @property
+    def plain(self) -> bool:
+        return self.bias is None and self.post_gain is None
 
 
 class ResidualStream:
@@ -75,11 +104,15 @@ class ResidualStream:
     def __init__(self, residual: torch.Tensor):
         self.residual = residual
         self.pending: Optional[Branch] = None
+        # What else joins the residual at the next fold: float32 rows [N, d] and a vector [d].
+        self.add_rows: Optional[torch.Tensor] = None
+        self.add_vec: Optional[torch.Tensor] = None
+        self.embedding_output: Optional[torch.Tensor] = None   # kept by the model when a stream op asks
 
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {
     "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "arrangement": {},
-    "embedding": {}, "head": {},
+    "embedding": {}, "head": {}, "stream_op": {},
 }
 
 

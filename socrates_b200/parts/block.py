@@ -57,3 +57,66 @@ class PreNormBlock:
 
 
 register_part("arrangement", "pre_norm", lambda layer_spec, name="": PreNormBlock(layer_spec))
+
+
+class SandwichBlock:
+    """A block that norms every branch on both sides:
+    x = x + norm_1b(mixer(norm_1(x))); x = x + norm_2b(feed_forward(norm_2(x))).
+    A layer without a feed-forward has the first half only (two norms instead of four).
+
+    The norm after a branch costs no kernel of its own: the branch is left pending with
+    the gain and eps of its norm, and the kernel that folds it into the residual (the
+    next norm of this or the following layer, a stream op, or the final norm) norms the
+    branch's sum first."""
+
+    def __init__(self, layer_spec):
+        want = 4 if layer_spec.feed_forward is not None else 2
+        if len(layer_spec.norms) != want:
+            raise ValueError(f"a sandwich block with{'' if want == 4 else 'out'} a feed-forward has {want} norms")
+        pre = layer_spec.prefix
+        self.norms = [build_part("norm", s, pre + s.name) for s in layer_spec.norms]
+        self.mixer = build_part("mixer", layer_spec.mixer, pre + layer_spec.mixer.name)
+        self.feed_forward = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward = build_part("feed_forward", layer_spec.feed_forward,
+                                           pre + layer_spec.feed_forward.name)
+
+    def parts(self):
+        return [*self.norms, self.mixer, *([self.feed_forward] if self.feed_forward is not None else [])]
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        out: Dict[str, ParamSpec] = {}
+        for p in self.parts():
+            out.update(p.parameters())
+        return out
+
+    def bind(self, tensors: Mapping, dtype) -> None:
+        for p in self.parts():
+            p.bind(tensors, dtype)
+
+    @property
+    def supports_graph(self) -> bool:
+        return all(getattr(p, "supports_graph", True) for p in self.parts())
+
+    def cache_needs(self):
+        fn = getattr(self.mixer, "cache_needs", None)
+        return fn() if fn is not None else None
+
+    def streamed_weights(self):
+        return [*getattr(self.mixer, "streamed_weights", list)(),
+                *(getattr(self.feed_forward, "streamed_weights", list)() if self.feed_forward is not None else [])]
+
+    @staticmethod
+    def _normed_on_entry(branch, norm):
+        branch.post_gain, branch.post_eps = norm.gain, norm.eps
+        return branch
+
+    def forward(self, ctx, stream: ResidualStream, cache) -> None:
+        h = self.norms[0].apply(ctx, stream)
+        stream.pending = self._normed_on_entry(self.mixer.forward(ctx, h, cache), self.norms[1])
+        if self.feed_forward is not None:
+            h = self.norms[2].apply(ctx, stream)
+            stream.pending = self._normed_on_entry(self.feed_forward.forward(ctx, h), self.norms[3])
+
+
+register_part("arrangement", "sandwich_norm", lambda layer_spec, name="": SandwichBlock(layer_spec))

@@ -1,0 +1,83 @@
+"""Mixers made of mixers.
+
+"normed_mean": several mixers read the same input side by side; each output is RMS-normed
+over the model width with a plain gain of its own and the results are averaged:
+    out = (1 / n) * sum_i unit_rms(mixer_i(x)) * gain_i
+Each inner mixer is an ordinary registered mixer built from its own spec; its tensors sit
+under `<name><prefix_i>`, its gain is the tensor `<name><prefix_i>out`, and what it asks of
+the cache (pages, state slots) is passed through with the prefix in front of state names.
+The norms, the gains and the mean are one kernel that reads the inner products' partial sums.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Mapping
+
+import torch
+
+from ..cache.manager import CacheNeeds
+from ..kernels import ops
+from .base import Branch, ParamSpec, Part, build_part, register_part
+
+
+class NormedMean(Part):
+    out_buffer = "branch"
+
+    def __init__(self, spec, name):
+        super().__init__(spec, name)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.eps = float(p["eps"])
+        self.prefixes: List[str] = [str(s.name) for s in p["branches"]]
+        self.inner = [build_part("mixer", s, name + s.name) for s in p["branches"]]
+        if len(self.inner) != 2:
+            raise ValueError("the normed-mean kernel takes two branches")
+        for i, m in enumerate(self.inner):
+            m.out_buffer = f"branch.{i}"
+        self.gains = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        out: Dict[str, ParamSpec] = {}
+        for pre, m in zip(self.prefixes, self.inner):
+            out.update(m.parameters())
+            out[self.name + pre + "out"] = ParamSpec((self.hidden,), role="gain", init="gain")
+        return out
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
+        for m in self.inner:
+            m.bind(tensors, dtype)
+        self.gains = [tensors[self.name + pre + "out"] for pre in self.prefixes]
+
+    @property
+    def supports_graph(self) -> bool:
+        return all(getattr(m, "supports_graph", True) for m in self.inner)
+
+    def cache_needs(self) -> CacheNeeds:
+        paged, state = None, {}
+        for pre, m in zip(self.prefixes, self.inner):
+            n = m.cache_needs() if hasattr(m, "cache_needs") else None
+            if n is None:
+                continue
+            if n.paged is not None:
+                if paged is not None:
+                    raise ValueError("only one mixer of a group can keep pages")
+                paged = n.paged
+            for key, s in n.state_specs().items():
+                state[pre + key] = s
+        return CacheNeeds(paged=paged, state=state or None)
+
+    def streamed_weights(self):
+        return [w for m in self.inner for w in getattr(m, "streamed_weights", list)()]
+
+    def forward(self, ctx, x: torch.Tensor, cache) -> Branch:
+        N = x.shape[0]
+        parts = [m.forward(ctx, x, cache.sub(pre)) for pre, m in zip(self.prefixes, self.inner)]
+        if not all(b.plain for b in parts):
+            raise ValueError("an inner mixer's branch must be plain partial sums")
+        out = ctx.buffers.take_flat(self.out_buffer, N * self.hidden, torch.float32).view(1, N, self.hidden)
+        ops.normed_mean(out[0], parts[0].partial, self.gains[0], parts[1].partial, self.gains[1], self.eps,
+                        1.0 / len(parts))
+        return Branch(out)
+
+
+register_part("mixer", "normed_mean", NormedMean)

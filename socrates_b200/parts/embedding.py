@@ -13,7 +13,7 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from ..kernels import ops
-from .base import ParamSpec, Part, register_part
+from .base import ParamSpec, Part, ResidualStream, build_part, register_part
 from .linear import Linear
 
 
@@ -42,19 +42,20 @@ class LMHead(Part):
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
         self.tied_to: Optional[str] = spec.params.get("tied_to")
+        self.tensor = self.name + str(spec.params.get("suffix", "weight"))
         self.linear: Optional[Linear] = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
         if self.tied_to is not None:
             return {self.tied_to: ParamSpec((self.vocab, self.hidden))}
-        return {self.name + "weight": ParamSpec((self.vocab, self.hidden))}
+        return {self.tensor: ParamSpec((self.vocab, self.hidden))}
 
     def duplicates(self) -> Dict[str, str]:
         """A tied head reads the embedding; a file may still carry a copy under the head's name."""
-        return {self.name + "weight": self.tied_to} if self.tied_to is not None else {}
+        return {self.tensor: self.tied_to} if self.tied_to is not None else {}
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
-        self.linear = Linear(tensors[self.tied_to or self.name + "weight"])
+        self.linear = Linear(tensors[self.tied_to or self.tensor])
 
     def streamed_weights(self):
         return [self.linear.weight]
@@ -65,3 +66,33 @@ class LMHead(Part):
 
 register_part("embedding", "embedding", Embedding)
 register_part("head", "lm_head", LMHead)
+
+
+class NormedEmbedding(Part):
+    """x = norm(table[ids]): the looked-up rows are normed before they become the residual
+    stream.  The norm is a part of its own kind (`norm` in the spec); its output is
+    float32 in both engines, since it IS the residual."""
+
+    def __init__(self, spec, name):
+        super().__init__(spec, name)
+        self.vocab = int(spec.params["vocab_size"])
+        self.hidden = int(spec.params["hidden_size"])
+        self.tensor = self.name + str(spec.params.get("suffix", "weight"))
+        norm_spec = spec.params["norm"]
+        self.norm = build_part("norm", norm_spec, self.name + norm_spec.name)
+        self.table: Optional[torch.Tensor] = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        return {self.tensor: ParamSpec((self.vocab, self.hidden)), **self.norm.parameters()}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
+        self.table = tensors[self.tensor]
+        self.norm.bind(tensors, dtype)
+
+    def forward(self, ctx) -> torch.Tensor:
+        raw = ctx.buffers.take("embedded", ctx.num_tokens, (self.hidden,), torch.float32)
+        ops.embed(raw, self.table, ctx.token_ids, ctx.token_feedback)
+        return self.norm.apply(ctx, ResidualStream(raw), buffer="residual", out_dtype=torch.float32)
+
+
+register_part("embedding", "normed_embedding", NormedEmbedding)

@@ -55,3 +55,51 @@ class SwiGLU(Part):
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
+
+
+class DenseFF(Part):
+    """Two matrices with biases around one activation: down(act(up(x) + b_up)) + b_down.
+    `activation`: "relu_squared" (max(z, 0)^2), "gelu_tanh" or "silu", computed in float32.
+    Tensors: `<name>up`, `<name>up.b`, `<name>down`, `<name>down.b` (the suffixes can be
+    renamed through the spec).  The up bias and the activation are one kernel that reads the
+    product (its split-K partial sums where it was cut); the down bias travels with the
+    branch and is added when the branch is folded into the residual."""
+
+    def __init__(self, spec, name):
+        super().__init__(spec, name)
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.activation = str(spec.params.get("activation", "relu_squared"))
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {self.activation!r}; known: {sorted(ops.ACTIVATIONS)}")
+        self.bias = bool(spec.params.get("bias", True))
+        self.up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+        self.up_bias = self.down_bias = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        n = self.name
+        out = {n + "up": ParamSpec((self.inter, self.hidden)), n + "down": ParamSpec((self.hidden, self.inter))}
+        if self.bias:
+            out[n + "up.b"] = ParamSpec((self.inter,), role="gain", init="normal")
+            out[n + "down.b"] = ParamSpec((self.hidden,), role="gain", init="normal")
+        return out
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
+        n = self.name
+        self.up, self.down = Linear(tensors[n + "up"]), Linear(tensors[n + "down"])
+        if self.bias:
+            self.up_bias, self.down_bias = tensors[n + "up.b"], tensors[n + "down.b"]
+
+    def streamed_weights(self):
+        return [self.up.weight, self.down.weight]
+
+    def forward(self, ctx, x: torch.Tensor) -> Branch:
+        N = x.shape[0]
+        u = self.up(ctx, x, "ff_up", out="model_or_partial")
+        act = ctx.buffers.take("act", N, (self.inter,), ctx.dtype)
+        ops.bias_act(act, u, self.up_bias, self.activation)
+        return Branch(self.down(ctx, act, "branch", out="partial"), bias=self.down_bias)
+
+
+register_part("feed_forward", "dense_act", DenseFF)

@@ -32,6 +32,9 @@ class Rotary(Part):
 
     def inv_freq(self) -> torch.Tensor:
         r = self.rotary_dim
+        if self.spec.params.get("table_precision") == "float64":
+            # theta^(-2j/r) in double precision, rounded once to float32
+            return (float(self.theta) ** (-torch.arange(0, r, 2, dtype=torch.float64) / r)).float()
         return 1.0 / (self.theta ** (torch.arange(0, r, 2).float() / r))
 
     def tables(self, device) -> Tuple[torch.Tensor, int]:

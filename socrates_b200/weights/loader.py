@@ -92,7 +92,7 @@ def load_weights(model_dir, expected: Mapping[str, ParamSpec], dtype: torch.dtyp
         if n in where:
             sl = where[n].get_slice(n)
             shape = tuple(sl.get_shape())
-            if shape != tuple(spec.shape):
+            if not spec.matches(shape):
                 wrong_shape.append(f"{n}: file has {shape}, model needs {tuple(spec.shape)}")
             st_dtype = sl.get_dtype()
             if spec.role in ("matrix", "gain") and st_dtype not in ("BF16", "F32", "F16"):

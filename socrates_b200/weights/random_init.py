@@ -34,9 +34,15 @@ def random_tensors(expected: Mapping[str, ParamSpec], seed: int,
     for name, spec in expected.items():
         g = _generator(seed, name)
         if spec.init == "gain":
-            out[name] = (1.0 + 0.1 * torch.randn(spec.shape, generator=g)).to(torch.float32)
+            out[name] = (1.0 + 0.1 * torch.randn(spec.draw_shape, generator=g)).to(torch.float32)
         elif spec.init == "normal":
-            out[name] = (0.02 * torch.randn(spec.shape, generator=g)).to(matrix_dtype)
+            out[name] = (0.02 * torch.randn(spec.draw_shape, generator=g)).to(
+                matrix_dtype if spec.role == "matrix" else torch.float32)
+        elif spec.init == "around_zero":
+            out[name] = (0.1 * torch.randn(spec.draw_shape, generator=g)).to(torch.float32)
+        elif spec.init == "uniform":
+            lo, hi = spec.bounds
+            out[name] = (lo + (hi - lo) * torch.rand(spec.draw_shape, generator=g)).to(torch.float32)
         else:
             raise ValueError(f"{name}: unknown init {spec.init!r}")
     return out
@@ -66,9 +72,16 @@ def random_tensors_on_device(expected: Mapping[str, ParamSpec], seed: int, dtype
     for i, (name, spec) in enumerate(expected.items()):
         g.manual_seed(seed * 1000003 + i)
         if spec.init == "gain":
-            out[name] = 1.0 + 0.1 * torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32)
+            out[name] = 1.0 + 0.1 * torch.randn(spec.draw_shape, generator=g, device=device, dtype=torch.float32)
+        elif spec.init == "around_zero":
+            out[name] = 0.1 * torch.randn(spec.draw_shape, generator=g, device=device, dtype=torch.float32)
+        elif spec.init == "uniform":
+            lo, hi = spec.bounds
+            out[name] = lo + (hi - lo) * torch.rand(spec.draw_shape, generator=g, device=device, dtype=torch.float32)
+        elif spec.role != "matrix":
+            out[name] = 0.02 * torch.randn(spec.draw_shape, generator=g, device=device, dtype=torch.float32)
         else:
-            t = torch.empty(spec.shape, device=device, dtype=dtype)
+            t = torch.empty(spec.draw_shape, device=device, dtype=dtype)
             t.normal_(0.0, 0.02, generator=g)
             out[name] = t
     return out
