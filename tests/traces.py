@@ -114,7 +114,7 @@ def run_trace(model_dir, dtype: str, trace: Trace, max_tokens: int, out_dir, env
     done = [l for l in proc.stdout.splitlines() if l.startswith("done ")]
     assert [int(l.split()[1]) for l in done] == list(range(len(trace.steps))), "a step was not acknowledged"
     cfg = json.loads((Path(model_dir) / "config.json").read_text())
-    V = cfg["vocab_size"]
+    V = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
     result = {}
     for step, rows in trace.expect.items():
         arr = np.fromfile(str(out_dir / f"{step}.f32"), dtype="<f4")
