@@ -382,10 +382,11 @@ def test_one_far_key_decides_retention(tmp_path, dtype):
         assert float((torch.cat(got) - want).abs().max() / want.abs().max()) < PART_TOL[dtype], sizes
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dtype", [torch.float32])
 def test_one_far_key_decides(tmp_path, dtype):
-    """Retention, layer 0 of P: one key 400 tokens back, planted in the dims that do not rotate of the head
-    with the slowest decay, is what the queries at the end mostly see.  Whole, and with the tail decoded."""
+    """The whole model P in float32 (where the tolerance is far below what the key contributes): one key
+    400 tokens back, planted in layer 0's retention, shows in the last logits.  Whole, and with the tail
+    decoded.  Both dtypes are covered on the part alone, above."""
     folder, cfg, w = make_folder(tmp_path, "P")
     key_tok, query_tok = 5, 9
     rows = [2 * 8 + 4, 2 * 8 + 5, 2 * 8 + 6, 2 * 8 + 7]           # head 2, dims 4..7 (rot.dims = 4)
