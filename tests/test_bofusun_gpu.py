@@ -417,18 +417,20 @@ def test_one_key_at_the_windows_edge_decides(tmp_path, dtype):
     w = _planted(folder, cfg, w, "l0.", "l0.mix.left.q", "l0.mix.left.k", list(range(16)), key_tok, query_tok, 9.0)
     others = [t for t in range(cfg["vocab"]) if t not in (key_tok, query_tok)]
     g = torch.Generator().manual_seed(3)
+    # the planted scores are large, and bfloat16 rounds them coarsely; a key wrongly seen or lost moves the logits by 0.5 and more
+    tol = TOL[dtype] if dtype == torch.float32 else 0.15
     for key_at in (15, 16, 40):
         ids = [others[int(i)] for i in torch.randint(0, len(others), (key_at + 60,), generator=g)]
         ids[key_at] = key_tok
         ids[key_at + 36] = query_tok          # the last query that sees the key
         ids[key_at + 37] = query_tok          # the first that does not
         ref = plain.forward(cfg, w, ids)
-        assert rel_err(ref[key_at + 36], ref[key_at + 37]) > 0.05           # the edge shows in the logits
+        assert rel_err(ref[key_at + 36], ref[key_at + 37]) > 0.5           # the edge shows in the logits
         h = Harness(folder, dtype)
-        assert rel_err(h.run("a", ids, (len(ids),)), ref) < TOL[dtype], key_at
-        assert rel_err(h.run("b", ids, (key_at + 20, 1)), ref) < TOL[dtype], key_at
-        assert rel_err(h.run("c", ids, (key_at + 1, 35, 2, 1)), ref) < TOL[dtype], key_at
-        assert rel_err(h.run("d", ids, (key_at + 36, 2, 1)), ref) < TOL[dtype], key_at
+        assert rel_err(h.run("a", ids, (len(ids),)), ref) < tol, key_at
+        assert rel_err(h.run("b", ids, (key_at + 20, 1)), ref) < tol, key_at
+        assert rel_err(h.run("c", ids, (key_at + 1, 35, 2, 1)), ref) < tol, key_at
+        assert rel_err(h.run("d", ids, (key_at + 36, 2, 1)), ref) < tol, key_at
 
 
 # ------------------------------------------------------------------------------------------
