@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 4b|8b|32b]
+    python bench.py --compare bofusun [--sizes 1k,2k,4k]     (another design beside Qwen3 at equal size)
 
 Default run: the layer sizes of the Qwen3-4B shape (36 layers, hidden 2560, 32 query
 heads over 8 KV heads, head_dim 128, intermediate 9728, vocabulary 151936, tied head),
@@ -390,6 +391,154 @@ def run_serve(args, name, cfg_full):
     return 0
 
 
+def _bofusun(width, layers_ret, heads, window):
+    """A Bofusun configuration at real layer widths: retention layers (keys width/2, values width) around
+    one parallel layer (windowed attention beside a selective scan of twice the width) with a dense
+    feed-forward of four times the width; the middle layers run twice."""
+    ret = {"type": "retention", "mlp": None,
+           "mixer": {"heads": heads, "dim": width // (2 * heads), "vdim": width // heads,
+                     "rot": {"dims": width // (2 * heads), "base": 1e6},
+                     "decay": [1.0 - 2.0 ** (-5 - 6 * h / max(1, heads - 1)) for h in range(heads)]}}
+    par = {"type": "parallel", "mlp": {"kind": "dense", "ff": 4 * width},
+           "mixer": {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "conv": 3,
+                              "scale": 128 ** -0.5, "softcap": 30.0, "bias_max": 2048, "mask": {"size": window}},
+                     "right": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}}}
+    layers = [ret] * (layers_ret // 2) + [par] + [ret] * (layers_ret - layers_ret // 2)
+    return {"architecture": "Bofusun", "vocab": 32000, "width": width, "norm": {"eps": 1e-5}, "layers": layers,
+            "loop": {"start": 1, "stop": layers_ret // 2 + 1, "times": 2}}
+
+
+def _qwen3_like(width, runs, heads):
+    """The Qwen3 decoder at the same width, number of layer runs, head size and feed-forward width."""
+    return {"architectures": ["Qwen3ForCausalLM"], "vocab_size": 32000, "hidden_size": width,
+            "intermediate_size": 4 * width, "num_hidden_layers": runs, "num_attention_heads": heads,
+            "num_key_value_heads": max(1, heads // 4), "head_dim": 128, "rms_norm_eps": 1e-6, "rope_theta": 1e6,
+            "tie_word_embeddings": False, "max_position_embeddings": 40960}
+
+
+def run_compare(args):
+    """`--compare bofusun`: prefill and decode throughput of the Bofusun design at real layer widths (random
+    weights) beside the Qwen3 decoder at equal width, layer runs and head size.  One JSON line."""
+    import torch
+
+    from socrates_b200 import Engine
+    from socrates_b200.config import config_from_dict
+    from socrates_b200.engine.engine import build_random_model
+    from socrates_b200.engine.runner import SamplingArgs, StepEntry
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    K, W, B, ctx, T = args.steps, args.warmup, args.batch, args.context, 2048
+    gen = torch.Generator().manual_seed(0)
+    sizes = {"1k": (1024, 8), "2k": (2048, 16), "4k": (4096, 32)}
+    wanted = [x for x in (args.sizes.split(",") if args.sizes else ["1k", "2k"]) if x in sizes]
+    sampler = ClockSampler()
+    sampler.start()
+    t_begin = time.perf_counter()
+    rows_out, launches = {}, 0
+    for size in wanted:
+        width, heads = sizes[size]
+        bof = _bofusun(width, 5, heads, 1024)
+        runs = len(config_from_dict(bof).plan().order)
+        for label, cfg_dict in (("bofusun", bof), ("qwen3", _qwen3_like(width, runs, heads))):
+            config = config_from_dict(cfg_dict)
+            built = build_random_model(config, 0, torch.bfloat16, dev)
+            model = built[1]
+            pages_per_row = -(-(ctx + K + W + 64) // 16)
+            engine = Engine(built, device="cuda:0", dtype="bfloat16", compile=True, max_batch=B, max_len=8192,
+                            max_new_tokens=K + W + 32, block_size=16, num_blocks=B * pages_per_row + 8,
+                            token_budget=max(T, B))
+            cache, runner = engine.cache, engine.runner
+            V = model.plan.vocab_size
+            # decode: B rows at ctx tokens (pages and states hold whatever is there: the time is what counts)
+            for r in range(B):
+                cache.assign(r)
+                assert cache.reserve(r, ctx + K + W + 1)
+                cache.commit(r, ctx)
+            ids = torch.randint(0, V, (K + W, B), generator=gen).tolist()
+            sampling = [SamplingArgs() for _ in range(B)]
+
+            def one(i):
+                runner.step([StepEntry(r, [ids[i][r]], cache.lengths[r], [0]) for r in range(B)], sampling)
+                for r in range(B):
+                    cache.commit(r, cache.lengths[r] + 1)
+            for i in range(W):
+                one(i)
+            torch.cuda.synchronize()
+            before = runner.kernel_launches
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for i in range(W, W + K):
+                one(i)
+            e.record()
+            torch.cuda.synchronize()
+            decode_ms = s.elapsed_time(e) / K
+            launches += runner.kernel_launches - before
+            for r in range(B):
+                cache.release(r)
+            # prefill: one prompt of T tokens in one step
+            prompt = torch.randint(0, V, (T,), generator=gen).tolist()
+            times = []
+            for i in range(W + 3):
+                cache.assign(0)
+                assert cache.reserve(0, T)
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                s.record()
+                runner.step([StepEntry(0, prompt, 0, [T - 1])], [SamplingArgs()])
+                e.record()
+                torch.cuda.synchronize()
+                cache.release(0)
+                if i >= W:
+                    times.append(s.elapsed_time(e))
+            prefill_ms = sorted(times)[len(times) // 2]
+            params = sum(t.numel() for t in model_tensors(model))
+            rows_out[f"{label}_{size}"] = {
+                "width": width, "layer_runs": runs, "parameters_m": round(params / 1e6, 1),
+                "decode_tokens_per_s": round(B * 1000.0 / decode_ms, 1), "decode_ms_per_step": round(decode_ms, 4),
+                "prefill_tokens_per_s": round(T * 1000.0 / prefill_ms, 1), "prefill_ms": round(prefill_ms, 3)}
+            del engine, cache, runner, model
+            torch.cuda.empty_cache()
+    t_end = time.perf_counter()
+    sampler.stop()
+    first = rows_out[f"bofusun_{wanted[0]}"]
+    line = {"metric": f"decode tokens/s (Bofusun design, width {first['width']}, batch {B}, {ctx}-token contexts)",
+            "value": first["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+            "ms_per_step": first["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic: random weights, token ids uniform over the vocabulary",
+            "config": {"model": "Bofusun and Qwen3 decoders at equal width and layer runs", "global_batch": B,
+                       "seq_len": ctx, "prefill_tokens": T, "parallelism": "single GPU", "cuda_graph": True,
+                       "l2": "inputs larger than L2 at widths 2k and 4k; a step's weights at 1k are not"},
+            "clocks": sampler.summary(t_begin, t_end), "gpu_launches": launches, "impl": "ours", "compare": rows_out}
+    print(json.dumps(line))
+    return 0
+
+
+def model_tensors(model):
+    """Every weight tensor a bound model holds (for a parameter count)."""
+    seen, out = set(), []
+
+    def walk(obj, depth=0):
+        import torch
+        if isinstance(obj, torch.Tensor):
+            if obj.data_ptr() not in seen:
+                seen.add(obj.data_ptr())
+                out.append(obj)
+        elif isinstance(obj, (list, tuple)):
+            for x in obj:
+                walk(x, depth + 1)
+        elif isinstance(obj, dict):
+            for x in obj.values():
+                walk(x, depth + 1)
+        elif hasattr(obj, "__dict__") and depth < 6 and type(obj).__module__.startswith("socrates_b200"):
+            for k, x in vars(obj).items():
+                if k not in ("plan", "spec", "weight_successor"):
+                    walk(x, depth + 1)
+    walk([model.embedding, model.layers, model.stream_ops, model.final_norm, model.head])
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -410,6 +559,10 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
+    ap.add_argument("--compare", default=None, choices=("bofusun",),
+                    help="bofusun: the Bofusun design at real layer widths beside Qwen3 at equal size "
+                         "(prefill and decode); the default workload is not run")
+    ap.add_argument("--sizes", default=None, help="with --compare: widths to run, of 1k,2k,4k (default 1k,2k)")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -420,6 +573,8 @@ def main():
     args.context = args.context or ctx
     workload = args.workload or ("serve" if args.shape == "8b" else "decode")
 
+    if args.compare is not None:
+        return run_compare(args)
     if args.impl == "reference":
         sys.path.insert(0, str(ROOT / "baseline"))
         import reference_arm

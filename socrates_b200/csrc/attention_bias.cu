@@ -14,6 +14,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "attention_reduce.cuh"
 
 using namespace sb;
 
@@ -39,6 +40,9 @@ struct BiasAttnArgs {
     int L;
     int Hq, Hkv, Dk, Dv, BS, window;
     float scale, cap;
+    int NP;                    // key partitions (grid.z); > 1: results go to part_o / part_ml and are merged after
+    float* part_o;             // [N, Hq, NP, Dv]
+    float* part_ml;            // [N, Hq, NP, 2]: running maximum and sum
 };
 
 template <typename T>
@@ -52,7 +56,11 @@ __global__ void __launch_bounds__(THREADS) bias_attention_kernel(BiasAttnArgs a)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = a.Hq / a.Hkv, Dk = a.Dk, Dv = a.Dv, BS = a.BS;
     const int row = a.token_rows[n], pos = a.positions[n];
-    const int lo = (a.window > 0 && pos + 1 > a.window) ? pos + 1 - a.window : 0;
+    const int lo_all = (a.window > 0 && pos + 1 > a.window) ? pos + 1 - a.window : 0;
+    // this block's share of the visible keys lo_all..pos: equal counts, in order
+    const int per = (pos + 1 - lo_all + a.NP - 1) / a.NP;
+    const int lo = lo_all + (int)blockIdx.z * per;
+    const int hi = min(pos + 1, lo + per);          // exclusive
     const int* table = a.block_table + (size_t)row * a.table_width;
     const T* q = (const T*)a.q;
     const T* kp = (const T*)a.k_pool;
@@ -70,8 +78,8 @@ __global__ void __launch_bounds__(THREADS) bias_attention_kernel(BiasAttnArgs a)
 #pragma unroll
         for (int g = 0; g < HEADS; ++g) acc[g][0] = acc[g][1] = 0.f;
         __syncthreads();
-        for (int c0 = lo; c0 <= pos; c0 += KEYS) {
-            const int nk = min(KEYS, pos + 1 - c0);
+        for (int c0 = lo; c0 < hi; c0 += KEYS) {
+            const int nk = min(KEYS, hi - c0);
             // scores of one key per thread, for all heads of the pass
             if (tid < nk) {
                 const int key = c0 + tid;
@@ -137,14 +145,26 @@ __global__ void __launch_bounds__(THREADS) bias_attention_kernel(BiasAttnArgs a)
         for (int g = 0; g < HEADS; ++g) {
             if (g >= gn) continue;
             const int h = h0 + g;
-            float f = 1.0f / run_sum[g];
+            float f = 1.0f;                              // the gate scales the output, so it may scale every part
             if (a.gate) {
                 const float z = to_float(((const T*)a.gate)[(size_t)n * a.gate_stride + h]);
-                f *= 1.0f / (1.0f + expf(-z));
+                f = 1.0f / (1.0f + expf(-z));
             }
-            T* o = (T*)a.out + ((size_t)n * a.Hq + h) * Dv;
-            if (tid < Dv) o[tid] = from_float<T>(acc[g][0] * f);
-            if (tid + THREADS < Dv) o[tid + THREADS] = from_float<T>(acc[g][1] * f);
+            if (a.NP == 1) {
+                f *= 1.0f / run_sum[g];
+                T* o = (T*)a.out + ((size_t)n * a.Hq + h) * Dv;
+                if (tid < Dv) o[tid] = from_float<T>(acc[g][0] * f);
+                if (tid + THREADS < Dv) o[tid + THREADS] = from_float<T>(acc[g][1] * f);
+            } else {
+                const size_t slot = ((size_t)n * a.Hq + h) * a.NP + blockIdx.z;
+                float* o = a.part_o + slot * Dv;
+                if (tid < Dv) o[tid] = acc[g][0] * f;
+                if (tid + THREADS < Dv) o[tid + THREADS] = acc[g][1] * f;
+                if (tid == 0) {                          // an empty part has sum 0 and is skipped by the merge
+                    a.part_ml[slot * 2] = run_max[g];
+                    a.part_ml[slot * 2 + 1] = run_sum[g];
+                }
+            }
         }
     }
 }
@@ -155,8 +175,8 @@ extern "C" int sb_attention_bias(void* out, const void* q, const void* k_pool, c
                                  const int* block_table, int table_width, const int* token_rows,
                                  const int* positions, const void* gate, long long gate_stride,
                                  const float* dist_bias, int L, int N, int Hq, int Hkv, int Dk, int Dv,
-                                 int page_size, int window, float scale, float cap, int dtype,
-                                 cudaStream_t stream) {
+                                 int page_size, int window, float scale, float cap, int num_partitions,
+                                 float* part_o, float* part_ml, int dtype, cudaStream_t stream) {
     SB_REQUIRE(N >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0,
                "attention_bias: %d query heads are no multiple of %d KV heads", Hq, Hkv);
     SB_REQUIRE(Dk >= 1 && Dk <= DMAX && Dv >= 1 && Dv <= 2 * THREADS,
@@ -166,15 +186,29 @@ extern "C" int sb_attention_bias(void* out, const void* q, const void* k_pool, c
     SB_REQUIRE(window >= 0, "attention_bias: window %d is negative", window);
     SB_REQUIRE(dist_bias == nullptr || L >= 1, "attention_bias: a bias table needs a length");
     SB_REQUIRE(N <= 65535, "attention_bias: %d tokens exceed one launch", N);
+    SB_REQUIRE(num_partitions >= 1 && num_partitions <= 64 &&
+                   (num_partitions == 1 || (part_o != nullptr && part_ml != nullptr)),
+               "attention_bias: %d partitions (1 to 64; more than one needs scratch buffers)", num_partitions);
     if (N == 0) return 0;
     BiasAttnArgs a;
     a.out = out; a.q = q; a.k_pool = k_pool; a.v_pool = v_pool; a.block_table = block_table;
     a.table_width = table_width; a.token_rows = token_rows; a.positions = positions; a.gate = gate;
     a.gate_stride = gate_stride; a.dist_bias = dist_bias; a.L = L > 0 ? L : 1; a.Hq = Hq; a.Hkv = Hkv; a.Dk = Dk;
     a.Dv = Dv; a.BS = page_size; a.window = window; a.scale = scale; a.cap = cap;
-    dim3 grid(Hkv, N);
-    if (dtype == SB_F32) sb::launch(bias_attention_kernel<float>, grid, dim3(THREADS), 0, stream, a);
-    else if (dtype == SB_BF16) sb::launch(bias_attention_kernel<__nv_bfloat16>, grid, dim3(THREADS), 0, stream, a);
-    else SB_REQUIRE(false, "attention_bias: unknown dtype %d", dtype);
+    a.NP = num_partitions; a.part_o = part_o; a.part_ml = part_ml;
+    dim3 grid(Hkv, N, num_partitions), rgrid(Hq, N);
+    if (dtype == SB_F32) {
+        sb::launch(bias_attention_kernel<float>, grid, dim3(THREADS), 0, stream, a);
+        if (num_partitions > 1)
+            sb::launch(attn_reduce_kernel<float>, rgrid, dim3(128), 0, stream, (float*)out, (const float*)part_o,
+                       (const float*)part_ml, Hq, Dv, num_partitions);
+    } else if (dtype == SB_BF16) {
+        sb::launch(bias_attention_kernel<__nv_bfloat16>, grid, dim3(THREADS), 0, stream, a);
+        if (num_partitions > 1)
+            sb::launch(attn_reduce_kernel<__nv_bfloat16>, rgrid, dim3(128), 0, stream, (__nv_bfloat16*)out,
+                       (const float*)part_o, (const float*)part_ml, Hq, Dv, num_partitions);
+    } else {
+        SB_REQUIRE(false, "attention_bias: unknown dtype %d", dtype);
+    }
     SB_LAUNCH_CHECK();
 }

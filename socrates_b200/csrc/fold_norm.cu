@@ -47,7 +47,15 @@ __global__ void __launch_bounds__(256) fold_rmsnorm_kernel(FoldArgs a) {
         float ss = 0.f;
         for (int i = threadIdx.x; i < d; i += blockDim.x) {
             float b = 0.f;
-            for (int s = 0; s < a.S; ++s) b += a.delta[s * a.delta_stride + (size_t)r * d + i];
+            for (int s0 = 0; s0 < a.S; s0 += 16) {              // sixteen loads in flight, added in order
+                float p[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (s0 + j < a.S) p[j] = __ldg(a.delta + (size_t)(s0 + j) * a.delta_stride + (size_t)r * d + i);
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (s0 + j < a.S) b += p[j];
+            }
             if (a.branch_bias) b += a.branch_bias[i];
             row[i] = b;
             ss += b * b;
@@ -75,6 +83,90 @@ __global__ void __launch_bounds__(256) fold_rmsnorm_kernel(FoldArgs a) {
     for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<T>(row[i] * rinv * a.gain[i]);
 }
 
+// The same with 16-byte accesses (d a multiple of 4, aligned rows) and every partial sum of a column
+// in flight at once: with few rows (a decode step) the kernel is one or two round trips to L2 per
+// phase instead of one per partial sum and column.
+template <typename T>
+__global__ void __launch_bounds__(512) fold_rmsnorm_vec_kernel(FoldArgs a) {
+    sb::pdl_launch_dependents();
+    extern __shared__ float row[];          // d floats
+    __shared__ float scratch[33];
+    const int m = blockIdx.x, d4 = a.d / 4;
+    sb::pdl_wait();
+    const int r = a.row_index ? a.row_index[m] : m;
+    const bool branch = a.S > 0 || a.branch_bias != nullptr;
+    float4* row4 = reinterpret_cast<float4*>(row);
+    const size_t stride4 = a.delta_stride / 4;
+    float binv = 1.f;
+    if (branch) {
+        float ss = 0.f;
+        const float4* del4 = reinterpret_cast<const float4*>(a.delta) + (size_t)r * d4;
+        for (int i = threadIdx.x; i < d4; i += blockDim.x) {
+            float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s0 = 0; s0 < a.S; s0 += 16) {
+                float4 p[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (s0 + j < a.S) p[j] = __ldg(del4 + (size_t)(s0 + j) * stride4 + i);
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (s0 + j < a.S) { b.x += p[j].x; b.y += p[j].y; b.z += p[j].z; b.w += p[j].w; }
+            }
+            if (a.branch_bias) {
+                const float4 c = __ldg(reinterpret_cast<const float4*>(a.branch_bias) + i);
+                b.x += c.x; b.y += c.y; b.z += c.z; b.w += c.w;
+            }
+            row4[i] = b;
+            ss += b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+        }
+        if (a.branch_gain) {
+            const float total = block_sum(ss, scratch);
+            binv = 1.0f / sqrtf(total / (float)a.d + a.branch_eps);
+        }
+    }
+    float4* res4 = reinterpret_cast<float4*>(a.residual + (size_t)r * a.d);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
+        float4 v = res4[i];
+        if (branch) {
+            float4 b = row4[i];
+            if (a.branch_gain) {
+                const float4 g = __ldg(reinterpret_cast<const float4*>(a.branch_gain) + i);
+                b.x *= binv * g.x; b.y *= binv * g.y; b.z *= binv * g.z; b.w *= binv * g.w;
+            }
+            v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+        }
+        if (a.add_rows) {
+            const float4 c = reinterpret_cast<const float4*>(a.add_rows + (size_t)r * a.d)[i];
+            v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+        }
+        if (a.add_vec) {
+            const float4 c = __ldg(reinterpret_cast<const float4*>(a.add_vec) + i);
+            v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+        }
+        row4[i] = v;
+        if (a.write_residual) res4[i] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    if (a.out == nullptr) return;
+    const float total = block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(total / (float)a.d + a.eps);
+    T* o = (T*)a.out + (size_t)m * a.d;
+    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
+        const float4 v = row4[i], g = __ldg(reinterpret_cast<const float4*>(a.gain) + i);
+        const float x0 = v.x * rinv * g.x, x1 = v.y * rinv * g.y, x2 = v.z * rinv * g.z, x3 = v.w * rinv * g.w;
+        if constexpr (sizeof(T) == 2) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(x0, x1), hi = __floats2bfloat162_rn(x2, x3);
+            uint2 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(o + 4 * i) = pk;
+        } else {
+            *reinterpret_cast<float4*>(o + 4 * i) = make_float4(x0, x1, x2, x3);
+        }
+    }
+}
+
 struct MeanArgs {
     const float* x[2];
     int S[2];
@@ -97,7 +189,15 @@ __global__ void __launch_bounds__(256) normed_mean_kernel(MeanArgs a) {
         float ss = 0.f;
         for (int i = threadIdx.x; i < d; i += blockDim.x) {
             float b = 0.f;
-            for (int s = 0; s < a.S[t]; ++s) b += a.x[t][s * a.stride[t] + (size_t)r * d + i];
+            for (int s0 = 0; s0 < a.S[t]; s0 += 16) {          // sixteen loads in flight, added in order
+                float p[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (s0 + j < a.S[t]) p[j] = __ldg(a.x[t] + (size_t)(s0 + j) * a.stride[t] + (size_t)r * d + i);
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (s0 + j < a.S[t]) b += p[j];
+            }
             rows[t * d + i] = b;
             ss += b * b;
         }
@@ -158,6 +258,26 @@ extern "C" int sb_fold_rmsnorm(float* residual, const float* delta, int S, long 
     a.d = d; a.eps = eps;
     a.write_residual = row_index == nullptr &&
                        (S > 0 || branch_bias != nullptr || add_rows != nullptr || add_vec != nullptr);
+    auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool vec = d % 4 == 0 && delta_stride % 4 == 0 && aligned(residual) && aligned(delta) && aligned(branch_bias) &&
+                     aligned(branch_gain) && aligned(add_rows) && aligned(add_vec) && aligned(gain) && aligned(out);
+    if (vec) {
+        int threads = ((d / 4 + 31) / 32) * 32;
+        if (threads > 512) threads = 512;
+        if (M > 512 && threads > 256) threads = 256;
+        if (out_dtype == SB_F32) {
+            if (smem > 48 * 1024)
+                cudaFuncSetAttribute(fold_rmsnorm_vec_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            sb::launch(fold_rmsnorm_vec_kernel<float>, dim3(M), dim3(threads), smem, stream, a);
+        } else if (out_dtype == SB_BF16) {
+            if (smem > 48 * 1024)
+                cudaFuncSetAttribute(fold_rmsnorm_vec_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            sb::launch(fold_rmsnorm_vec_kernel<__nv_bfloat16>, dim3(M), dim3(threads), smem, stream, a);
+        } else {
+            SB_REQUIRE(false, "fold_rmsnorm: unknown dtype %d", out_dtype);
+        }
+        SB_LAUNCH_CHECK();
+    }
     if (out_dtype == SB_F32) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(fold_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

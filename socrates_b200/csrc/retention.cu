@@ -124,16 +124,240 @@ int launch_retention(const RetArgs& a, int R, int threads, int rpt, size_t smem,
     return 1;
 }
 
+
+// ----------------------------------------------------------------------------------------
+// The same recurrence for prompt portions, a chunk of C tokens at a time.  With S0 the state
+// before the chunk and t, s counting tokens inside it:
+//   o_t = decay^(t+1) * S0^T q_t + sum_{s<=t} decay^(t-s) (q_t . k_s) v_s
+//   S_C = decay^C * S0 + sum_s decay^(C-1-s) k_s v_s^T
+// so the tokens of a chunk are independent of one another and a block of 256 threads works on
+// all of them at once; chunks follow one another through the state, which stays in shared
+// memory.  Scores, decays and sums are float32 on the CUDA cores.  One block per (request, head).
+// Warp w owns the tokens t = w, w + 8, ... of a chunk (and the state rows i = w, w + 8, ... in the
+// update); lane l owns the value columns j = l, l + 32, ...
+struct RetChunkArgs {
+    RetArgs r;
+    int C;               // tokens per chunk: 16, 32 or 64
+};
+
+constexpr int TB = 4;      // tokens (or state rows) a warp works on at once
+
+template <typename T, int JJ>
+__global__ void __launch_bounds__(256) retention_chunk_kernel(RetChunkArgs ca) {
+    sb::pdl_launch_dependents();
+    const RetArgs& a = ca.r;
+    extern __shared__ float sm[];
+    const int dk = a.dk, dv = a.dv, C = ca.C, kst = dk + 1;
+    float* Ss = sm;                         // [dk][dv]   the state
+    float* Qs = Ss + dk * dv;               // [C][dk]
+    float* Ks = Qs + C * dk;                // [C][dk+1]
+    float* Vs = Ks + C * kst;               // [C][dv]
+    float* As = Vs + C * dv;                // [C][C]     decayed scores
+    float* pw = As + C * C;                 // [C+1]      powers of the decay
+    const int r = blockIdx.y, h = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const float decay = a.decay[h];
+    const int half = a.rot / 2;
+    if (tid == 0) {
+        float p = 1.f;
+        for (int n = 0; n <= C; ++n) { pw[n] = p; p *= decay; }
+    }
+    sb::pdl_wait();
+    const int n0 = a.seq_starts[r], n1 = a.seq_starts[r + 1];
+    const int row = a.seq_rows[r], first = a.seq_first_pos[r];
+    float* S = a.state + (((size_t)row * a.H + h) * dk) * dv;
+    for (int i = tid; i < dk * dv; i += 256) Ss[i] = S[i];
+    const T* in = (const T*)a.qkvg;
+    for (int c0 = n0; c0 < n1; c0 += C) {
+        const int len = min(C, n1 - c0);
+        __syncthreads();                    // the last chunk's readers are done with Q, K, V and A
+        // ---- this chunk's rotated q and k (scaled), and v
+        for (int idx = tid; idx < len * dk; idx += 256) {
+            const int t = idx / dk, i = idx - t * dk;
+            const T* tok = in + (size_t)(c0 + t) * a.stride;
+            if (i < half) {
+                const float ang = (float)(first + (c0 - n0) + t) * a.inv_freq[i];
+                const float c = cosf(ang), sn = sinf(ang);
+                const float qu = to_float(tok[a.q_off + h * dk + i]), qv = to_float(tok[a.q_off + h * dk + i + half]);
+                const float ku = to_float(tok[a.k_off + h * dk + i]), kv = to_float(tok[a.k_off + h * dk + i + half]);
+                Qs[t * dk + i] = qu * c - qv * sn;
+                Qs[t * dk + i + half] = qv * c + qu * sn;
+                Ks[t * kst + i] = (ku * c - kv * sn) * a.k_scale;
+                Ks[t * kst + i + half] = (kv * c + ku * sn) * a.k_scale;
+            } else if (i >= a.rot) {
+                Qs[t * dk + i] = to_float(tok[a.q_off + h * dk + i]);
+                Ks[t * kst + i] = to_float(tok[a.k_off + h * dk + i]) * a.k_scale;
+            }
+        }
+        for (int idx = tid; idx < len * dv; idx += 256) {
+            const int t = idx / dv, j = idx - t * dv;
+            Vs[t * dv + j] = to_float(in[(size_t)(c0 + t) * a.stride + a.v_off + h * dv + j]);
+        }
+        __syncthreads();
+        // ---- decayed scores A[t][s] = (q_t . k_s) decay^(t-s) for s <= t, zero above the diagonal
+        for (int t = warp; t < len; t += 8) {
+            for (int s0 = 0; s0 < C; s0 += 32) {
+                const int s = s0 + lane;
+                float dot = 0.f;
+                if (s <= t) {
+                    const float* qr = Qs + t * dk;
+                    const float* kr = Ks + s * kst;
+                    for (int i = 0; i < dk; ++i) dot = fmaf(qr[i], kr[i], dot);
+                    dot *= pw[t - s];
+                }
+                if (s < C) As[t * C + s] = dot;
+            }
+        }
+        __syncthreads();
+        // ---- outputs, four tokens of the warp at a time (a value of the state or of v serves all four)
+        for (int t0 = warp; t0 < len; t0 += 8 * TB) {
+            float acc[TB][JJ], inter[TB][JJ];
+#pragma unroll
+            for (int k = 0; k < TB; ++k)
+#pragma unroll
+                for (int jj = 0; jj < JJ; ++jj) acc[k][jj] = inter[k][jj] = 0.f;
+            int tk[TB];
+#pragma unroll
+            for (int k = 0; k < TB; ++k) tk[k] = min(t0 + 8 * k, len - 1);      // rows past the end repeat the last one and are not written
+            for (int i = 0; i < dk; ++i) {
+                float qi[TB];
+#pragma unroll
+                for (int k = 0; k < TB; ++k) qi[k] = Qs[tk[k] * dk + i];
+#pragma unroll
+                for (int jj = 0; jj < JJ; ++jj) {
+                    const int j = lane + 32 * jj;
+                    const float sv = j < dv ? Ss[i * dv + j] : 0.f;
+#pragma unroll
+                    for (int k = 0; k < TB; ++k) inter[k][jj] = fmaf(qi[k], sv, inter[k][jj]);
+                }
+            }
+            const int last = tk[TB - 1];
+            for (int s = 0; s <= last; ++s) {
+                float w[TB];
+#pragma unroll
+                for (int k = 0; k < TB; ++k) w[k] = As[tk[k] * C + s];
+#pragma unroll
+                for (int jj = 0; jj < JJ; ++jj) {
+                    const int j = lane + 32 * jj;
+                    const float vv = j < dv ? Vs[s * dv + j] : 0.f;
+#pragma unroll
+                    for (int k = 0; k < TB; ++k) acc[k][jj] = fmaf(w[k], vv, acc[k][jj]);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < TB; ++k) {
+                const int t = t0 + 8 * k;
+                if (t >= len) break;
+                float ss = 0.f;
+#pragma unroll
+                for (int jj = 0; jj < JJ; ++jj) {
+                    acc[k][jj] = fmaf(pw[t + 1], inter[k][jj], acc[k][jj]);
+                    if (lane + 32 * jj < dv) ss += acc[k][jj] * acc[k][jj];
+                }
+                ss = warp_sum(ss);
+                const float rinv = 1.0f / sqrtf(ss / (float)dv + a.eps);
+                const T* tok = in + (size_t)(c0 + t) * a.stride;
+#pragma unroll
+                for (int jj = 0; jj < JJ; ++jj) {
+                    const int j = lane + 32 * jj;
+                    if (j < dv) {
+                        const float g = to_float(tok[a.g_off + h * dv + j]);
+                        ((T*)a.out)[((size_t)(c0 + t) * a.H + h) * dv + j] =
+                            from_float<T>(acc[k][jj] * rinv * (g / (1.0f + expf(-g))));
+                    }
+                }
+            }
+        }
+        __syncthreads();                    // every reader of the old state is done
+        // ---- the state moves on by the chunk, four rows of the warp at a time
+        for (int i0 = warp; i0 < dk; i0 += 8 * TB) {
+            float acc[TB][JJ];
+#pragma unroll
+            for (int k = 0; k < TB; ++k)
+#pragma unroll
+                for (int jj = 0; jj < JJ; ++jj) acc[k][jj] = 0.f;
+            int ik[TB];
+#pragma unroll
+            for (int k = 0; k < TB; ++k) ik[k] = min(i0 + 8 * k, dk - 1);
+            for (int s = 0; s < len; ++s) {
+                const float p = pw[len - 1 - s];
+                float w[TB];
+#pragma unroll
+                for (int k = 0; k < TB; ++k) w[k] = Ks[s * kst + ik[k]] * p;
+#pragma unroll
+                for (int jj = 0; jj < JJ; ++jj) {
+                    const int j = lane + 32 * jj;
+                    const float vv = j < dv ? Vs[s * dv + j] : 0.f;
+#pragma unroll
+                    for (int k = 0; k < TB; ++k) acc[k][jj] = fmaf(w[k], vv, acc[k][jj]);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < TB; ++k) {
+                const int i = i0 + 8 * k;
+                if (i >= dk) break;
+#pragma unroll
+                for (int jj = 0; jj < JJ; ++jj) {
+                    const int j = lane + 32 * jj;
+                    if (j < dv) Ss[i * dv + j] = fmaf(pw[len], Ss[i * dv + j], acc[k][jj]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < dk * dv; i += 256) S[i] = Ss[i];
+}
+
+template <typename T>
+int launch_retention_chunked(const RetArgs& a, int R, int C, size_t smem, cudaStream_t stream) {
+    RetChunkArgs ca;
+    ca.r = a;
+    ca.C = C;
+    dim3 grid(a.H, R);
+    static sb::OncePerDevice once[3];
+#define SB_RETC(JJ_, K_)                                                                                   \
+    if (a.dv <= 32 * JJ_) {                                                                                \
+        if (!once[K_].flag()) {                                                                            \
+            cudaFuncSetAttribute(retention_chunk_kernel<T, JJ_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            once[K_].flag() = true;                                                                        \
+        }                                                                                                  \
+        sb::launch(retention_chunk_kernel<T, JJ_>, grid, dim3(256), smem, stream, ca);                    \
+        return 0;                                                                                          \
+    }
+    SB_RETC(2, 0) SB_RETC(4, 1) SB_RETC(8, 2)
+#undef SB_RETC
+    return 1;
+}
+
 }  // namespace
 
 extern "C" int sb_retention(const void* qkvg, long long stride, int q_off, int k_off, int v_off, int g_off,
                             float* state, const float* decay, const float* inv_freq, int rot, void* out,
                             const int* seq_starts, const int* seq_rows, const int* seq_first_pos, int R, int H,
-                            int dk, int dv, float eps, float k_scale, int dtype, cudaStream_t stream) {
+                            int dk, int dv, float eps, float k_scale, int chunked, int dtype, cudaStream_t stream) {
     SB_REQUIRE(R >= 0 && H > 0 && dk > 0 && dv > 0 && dv <= 512, "retention: bad sizes R=%d H=%d dk=%d dv=%d", R, H, dk, dv);
     SB_REQUIRE(rot >= 0 && rot <= dk && rot % 2 == 0, "retention: %d rotating dims of %d", rot, dk);
     SB_REQUIRE(R <= 65535, "retention: %d requests exceed one launch", R);
     if (R == 0) return 0;
+    if (chunked) {
+        // prompt portions: chunks of as many tokens as fit a block's shared memory beside the state
+        RetArgs a;
+        a.qkvg = qkvg; a.stride = stride; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off; a.g_off = g_off;
+        a.state = state; a.decay = decay; a.inv_freq = inv_freq; a.rot = rot; a.out = out;
+        a.seq_starts = seq_starts; a.seq_rows = seq_rows; a.seq_first_pos = seq_first_pos;
+        a.H = H; a.dk = dk; a.dv = dv; a.P = 1; a.eps = eps; a.k_scale = k_scale;
+        int C = 64;
+        auto need = [&](int c) { return (size_t)(dk * dv + c * dk + c * (dk + 1) + c * dv + c * c + c + 1) * sizeof(float); };
+        while (C > 16 && need(C) > 200 * 1024) C /= 2;
+        if (need(C) <= 200 * 1024 && dv <= 256) {
+            int bad = 1;
+            if (dtype == SB_F32) bad = launch_retention_chunked<float>(a, R, C, need(C), stream);
+            else if (dtype == SB_BF16) bad = launch_retention_chunked<__nv_bfloat16>(a, R, C, need(C), stream);
+            SB_REQUIRE(!bad, "retention: no chunked kernel for dv=%d or dtype %d", dv, dtype);
+            SB_LAUNCH_CHECK();
+        }
+        // a head too large for shared memory falls through to the token-by-token kernel
+    }
     int P = 256 / dv;
     if (P < 1) P = 1;
     if (P > dk) P = dk;

@@ -19,7 +19,7 @@ using namespace sb;
 namespace {
 
 constexpr int THREADS = 128;
-constexpr int TOKENS = 8;        // tokens whose B and C are staged at once
+constexpr int TOKENS = 16;       // tokens whose B and C are staged (and whose dt, x, z are loaded) at once
 constexpr int NPT = 8;           // states per thread at most
 
 struct ScanArgs {
@@ -78,14 +78,25 @@ __global__ void __launch_bounds__(THREADS) selective_scan_kernel(ScanArgs a) {
             bcs[i] = to_float(bc[(size_t)(t0 + t) * a.bc_stride + k]);
         }
         __syncthreads();
-        for (int t = 0; t < nt; ++t) {
-            const int n = t0 + t;
-            float dt = 0.f, xv = 0.f;
-            if (live) {
-                const float raw = a.dt_raw[(size_t)n * a.inner + c] + bias;
-                dt = raw > 20.f ? raw : log1pf(expf(raw));
-                xv = to_float(xs[(size_t)n * a.x_stride + c]);
+        // the tokens' own values: all loads go out before the first is used (one round trip for the batch)
+        float raws[TOKENS], xvs[TOKENS], zvs[TOKENS];
+#pragma unroll
+        for (int t = 0; t < TOKENS; ++t) {
+            raws[t] = xvs[t] = zvs[t] = 0.f;
+            if (live && t < nt) {
+                const int n = t0 + t;
+                raws[t] = a.dt_raw[(size_t)n * a.inner + c];
+                xvs[t] = to_float(xs[(size_t)n * a.x_stride + c]);
+                if (l == 0) zvs[t] = to_float(zs[(size_t)n * a.z_stride + c]);
             }
+        }
+#pragma unroll
+        for (int t = 0; t < TOKENS; ++t) {
+            if (t >= nt) break;
+            const int n = t0 + t;
+            const float raw = raws[t] + bias;
+            const float dt = live ? (raw > 20.f ? raw : log1pf(expf(raw))) : 0.f;
+            const float xv = xvs[t];
             const float* Bt = bcs + t * 2 * states;
             const float* Ct = Bt + states;
             const float dx = dt * xv;
@@ -101,7 +112,7 @@ __global__ void __launch_bounds__(THREADS) selective_scan_kernel(ScanArgs a) {
             for (int o = TS >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
             if (live && l == 0) {
                 y += Dc * xv;
-                const float zv = to_float(zs[(size_t)n * a.z_stride + c]);
+                const float zv = zvs[t];
                 ((T*)a.out)[(size_t)n * a.inner + c] = from_float<T>(y * (zv / (1.0f + expf(-zv))));
             }
         }

@@ -621,11 +621,14 @@ def short_conv_tail(tail: torch.Tensor, x: torch.Tensor, in_bias: Optional[torch
 
 def retention(out: torch.Tensor, qkvg: torch.Tensor, offsets: Tuple[int, int, int, int], state: torch.Tensor,
               decay: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, seq_starts: torch.Tensor,
-              seq_rows: torch.Tensor, seq_first_pos: torch.Tensor, eps: float, k_scale: float) -> None:
+              seq_rows: torch.Tensor, seq_first_pos: torch.Tensor, eps: float, k_scale: float,
+              chunked: bool = False) -> None:
     """Decayed linear attention of every request's tokens of the step, in order, through its state slot.
 
     qkvg [N, width] holds q, k (H x dk each), v and g (H x dv each) at the column `offsets`; state float32
-    [rows, H, dk, dv] is read and left advanced; out [N, H*dv] = unit_rms(S^T q) * silu(g) per head."""
+    [rows, H, dk, dv] is read and left advanced; out [N, H*dv] = unit_rms(S^T q) * silu(g) per head.
+    `chunked`: the kernel for prompt portions, which works on up to 64 tokens of a request at once (the same
+    sums in another order); without it every token is a step of the recurrence, which is what a decode step wants."""
     N = qkvg.shape[0]
     _, H, dk, dv = state.shape
     R = seq_rows.numel()
@@ -642,8 +645,8 @@ def retention(out: torch.Tensor, qkvg: torch.Tensor, offsets: Tuple[int, int, in
     lib = library()
     check(lib, lib.sb_retention(_ptr(qkvg), qkvg.stride(0), *[int(o) for o in offsets], _ptr(state), _ptr(decay),
                                 _ptr(inv_freq), int(rotary_dim), _ptr(out), _ptr(seq_starts), _ptr(seq_rows),
-                                _ptr(seq_first_pos), R, H, dk, dv, float(eps), float(k_scale), _code(out.dtype),
-                                _stream()), "retention")
+                                _ptr(seq_first_pos), R, H, dk, dv, float(eps), float(k_scale), int(chunked),
+                                _code(out.dtype), _stream()), "retention")
 
 
 def selective_scan(out: torch.Tensor, x: torch.Tensor, z: torch.Tensor, dt_raw: torch.Tensor,
@@ -679,11 +682,15 @@ def selective_scan(out: torch.Tensor, x: torch.Tensor, z: torch.Tensor, dt_raw: 
 def attention_bias(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                    block_table: torch.Tensor, token_rows: torch.Tensor, positions: torch.Tensor, num_heads: int,
                    scale: float, window: int = 0, softcap: float = 0.0,
-                   dist_bias: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
+                   dist_bias: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                   num_partitions: int = 1, part_o: Optional[torch.Tensor] = None,
+                   part_ml: Optional[torch.Tensor] = None) -> None:
     """Paged causal attention, one query per token, with scores capped by softcap * tanh(s / softcap)
     (0: no cap), a float32 bias table [Hq, L] by distance (distances past L-1 use the last entry) and a
     sigmoid gate per head (gate [N, >= Hq], head h at column h).  Keys and values may have different head
-    sizes: q [N, Hq*Dk], k_pool [pages, Hkv, BS, Dk], v_pool [pages, Hkv, BS, Dv], out [N, Hq*Dv]."""
+    sizes: q [N, Hq*Dk], k_pool [pages, Hkv, BS, Dk], v_pool [pages, Hkv, BS, Dv], out [N, Hq*Dv].
+    With `num_partitions` > 1 every token's visible keys are cut into that many equal shares, one block
+    each, merged by a second kernel through the float32 scratch part_o (N*Hq*NP*Dv) and part_ml (N*Hq*NP*2)."""
     N = q.shape[0]
     pages, Hkv, BS, Dk = k_pool.shape
     Dv = v_pool.shape[3]
@@ -706,8 +713,15 @@ def attention_bias(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_p
         if gate.dtype != q.dtype or gate.dim() != 2 or gate.shape[0] != N or gate.shape[1] < Hq or gate.stride(1) != 1:
             raise KernelError(f"gate must be [{N}, >= {Hq}] in {q.dtype} with unit column stride")
         gate_stride = gate.stride(0)
+    if num_partitions > 1:
+        _want(part_o, "part_o", torch.float32)
+        _want(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < N * Hq * num_partitions * Dv or part_ml.numel() < N * Hq * num_partitions * 2:
+            raise KernelError("attention scratch buffers are too small")
     lib = library()
     check(lib, lib.sb_attention_bias(_ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
                                      block_table.shape[1], _ptr(token_rows), _ptr(positions), _ptr(gate), gate_stride,
                                      _ptr(dist_bias), L, N, Hq, Hkv, Dk, Dv, BS, int(window), float(scale),
-                                     float(softcap), _code(q.dtype), _stream()), "attention_bias")
+                                     float(softcap), int(num_partitions), _ptr(part_o), _ptr(part_ml),
+                                     _code(q.dtype), _stream()), "attention_bias",
+          kernels=2 if num_partitions > 1 else 1)

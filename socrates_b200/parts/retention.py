@@ -69,7 +69,7 @@ class Retention(Part):
         inv_freq, rotary_dim = self.position.tables(x.device)
         offsets = (0, H * self.dk, 2 * H * self.dk, 2 * H * self.dk + H * self.dv)
         ops.retention(y, qkvg, offsets, cache.state(), self.decay_t, inv_freq, rotary_dim, ctx.seq_starts,
-                      ctx.seq_rows, ctx.seq_first_pos, self.eps, self.key_scale)
+                      ctx.seq_rows, ctx.seq_first_pos, self.eps, self.key_scale, chunked=not ctx.all_decode)
         return Branch(self.o(ctx, y, self.out_buffer, out="partial"))
 
 

@@ -101,6 +101,15 @@ class WindowBiasAttention(Part):
     def streamed_weights(self):
         return [self.qkvg.weight, self.o.weight]
 
+    def partitions(self, ctx, N: int, max_len: int) -> int:
+        """Into how many shares each token's visible keys are cut: with few tokens (a decode step) one block
+        per (token, KV head) leaves the GPU idle, so the keys are shared out over about four blocks an SM, at
+        least 64 keys a share, at most 16 shares.  A function of the token count and of limits alone (a
+        recorded graph stays valid); it changes the order of additions, nothing else."""
+        span = min(self.window or max_len, max_len)
+        blocks = max(1, N * self.G)
+        return max(1, min(16, (4 * ctx.num_sms) // blocks, -(-span // 64)))
+
     def forward(self, ctx, x: torch.Tensor, cache) -> Branch:
         N = x.shape[0]
         qkvg = self.qkvg(ctx, x, "wa_qkvg")
@@ -114,8 +123,13 @@ class WindowBiasAttention(Part):
         if tail is not None:
             ops.short_conv_tail(tail, qkvg, self.in_bias, self.taps, ctx.seq_starts, ctx.seq_rows)
         attn = ctx.buffers.take("wa_attn", N, (self.H * self.dv,), ctx.dtype)
+        NP, part_o, part_ml = self.partitions(ctx, N, cache.manager.max_len), None, None
+        if NP > 1:
+            part_o = ctx.buffers.take_flat("attn_part_o", N * self.H * NP * self.dv, torch.float32)
+            part_ml = ctx.buffers.take_flat("attn_part_ml", N * self.H * NP * 2, torch.float32)
         ops.attention_bias(attn, q, k_pool, v_pool, table, ctx.token_rows, ctx.positions, self.H, self.scale,
-                           self.window or 0, self.softcap, self.dist_bias, gate=qkvg[:, self.C:self.C + self.H])
+                           self.window or 0, self.softcap, self.dist_bias, gate=qkvg[:, self.C:self.C + self.H],
+                           num_partitions=NP, part_o=part_o, part_ml=part_ml)
         return Branch(self.o(ctx, attn, self.out_buffer, out="partial"))
 
 
