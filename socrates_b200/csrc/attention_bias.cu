@@ -52,6 +52,7 @@ __global__ void __launch_bounds__(THREADS) bias_attention_kernel(BiasAttnArgs a)
     __shared__ float qs[HEADS][DMAX];
     __shared__ float w[HEADS][KEYS];
     __shared__ float run_max[HEADS], run_sum[HEADS], rescale[HEADS];
+    __shared__ int pg[KEYS];               // the page of every key of the chunk
     const int kh = blockIdx.x, n = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = a.Hq / a.Hkv, Dk = a.Dk, Dv = a.Dv, BS = a.BS;
@@ -83,14 +84,31 @@ __global__ void __launch_bounds__(THREADS) bias_attention_kernel(BiasAttnArgs a)
             // scores of one key per thread, for all heads of the pass
             if (tid < nk) {
                 const int key = c0 + tid;
-                const T* kr = kp + (((size_t)table[key / BS] * a.Hkv + kh) * BS + key % BS) * Dk;
+                const int page = table[key / BS];
+                pg[tid] = page;
+                const T* kr = kp + (((size_t)page * a.Hkv + kh) * BS + key % BS) * Dk;
                 float dot[HEADS];
 #pragma unroll
                 for (int g = 0; g < HEADS; ++g) dot[g] = 0.f;
-                for (int d = 0; d < Dk; ++d) {
-                    const float kf = to_float(kr[d]);
+                constexpr int VEC = Vec16<T>::N;
+                if (Dk % VEC == 0 && (reinterpret_cast<uintptr_t>(kp) & 15) == 0) {
+#pragma unroll 4
+                    for (int d = 0; d < Dk; d += VEC) {         // 16-byte loads, several in flight
+                        Vec16<T> kv;
+                        kv.load(kr + d);
 #pragma unroll
-                    for (int g = 0; g < HEADS; ++g) dot[g] = fmaf(qs[g][d], kf, dot[g]);
+                        for (int e = 0; e < VEC; ++e) {
+                            const float kf = kv.get(e);
+#pragma unroll
+                            for (int g = 0; g < HEADS; ++g) dot[g] = fmaf(qs[g][d + e], kf, dot[g]);
+                        }
+                    }
+                } else {
+                    for (int d = 0; d < Dk; ++d) {
+                        const float kf = to_float(kr[d]);
+#pragma unroll
+                        for (int g = 0; g < HEADS; ++g) dot[g] = fmaf(qs[g][d], kf, dot[g]);
+                    }
                 }
                 const int dist = min(pos - key, a.L - 1);
 #pragma unroll
@@ -127,9 +145,10 @@ __global__ void __launch_bounds__(THREADS) bias_attention_kernel(BiasAttnArgs a)
             // weighted sum of the values: thread t owns dims t and t + THREADS
 #pragma unroll
             for (int g = 0; g < HEADS; ++g) { acc[g][0] *= rescale[g]; acc[g][1] *= rescale[g]; }
-            for (int t = 0; t < nk; ++t) {
+#pragma unroll 8
+            for (int t = 0; t < nk; ++t) {                      // the addresses come from shared memory: loads overlap
                 const int key = c0 + t;
-                const T* vr = vp + (((size_t)table[key / BS] * a.Hkv + kh) * BS + key % BS) * Dv;
+                const T* vr = vp + (((size_t)pg[t] * a.Hkv + kh) * BS + key % BS) * Dv;
                 const float v0 = tid < Dv ? to_float(vr[tid]) : 0.f;
                 const float v1 = tid + THREADS < Dv ? to_float(vr[tid + THREADS]) : 0.f;
 #pragma unroll

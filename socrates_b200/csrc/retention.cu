@@ -140,6 +140,31 @@ struct RetChunkArgs {
     int C;               // tokens per chunk: 16, 32 or 64
 };
 
+// rows x cols of T from global memory (row stride `src_stride` elements) to float32 shared memory (row
+// stride `dst_stride`), by the 256 threads of a block; 16-byte loads where the rows allow them.
+template <typename T>
+__device__ __forceinline__ void copy_rows(float* dst, int dst_stride, const T* src, long long src_stride, int rows,
+                                          int cols, int tid) {
+    constexpr int VEC = Vec16<T>::N;
+    if (cols % VEC == 0 && src_stride % VEC == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        const int per_row = cols / VEC, total = rows * per_row;
+#pragma unroll 4
+        for (int idx = tid; idx < total; idx += 256) {
+            const int t = idx / per_row, v = idx - t * per_row;
+            Vec16<T> x;
+            x.load(src + (size_t)t * src_stride + v * VEC);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) dst[t * dst_stride + v * VEC + e] = x.get(e);
+        }
+    } else {
+#pragma unroll 4
+        for (int idx = tid; idx < rows * cols; idx += 256) {
+            const int t = idx / cols, i = idx - t * cols;
+            dst[t * dst_stride + i] = to_float(src[(size_t)t * src_stride + i]);
+        }
+    }
+}
+
 constexpr int TB = 4;      // tokens (or state rows) a warp works on at once
 
 template <typename T, int JJ>
@@ -171,27 +196,26 @@ __global__ void __launch_bounds__(256) retention_chunk_kernel(RetChunkArgs ca) {
     for (int c0 = n0; c0 < n1; c0 += C) {
         const int len = min(C, n1 - c0);
         __syncthreads();                    // the last chunk's readers are done with Q, K, V and A
-        // ---- this chunk's rotated q and k (scaled), and v
+        // ---- this chunk's q, k and v as they come from the projection (copies with many loads in
+        // flight: nothing here depends on a loaded value), then q and k rotated in place and k scaled
+        copy_rows(Qs, dk, in + (size_t)c0 * a.stride + a.q_off + h * dk, a.stride, len, dk, tid);
+        copy_rows(Ks, kst, in + (size_t)c0 * a.stride + a.k_off + h * dk, a.stride, len, dk, tid);
+        copy_rows(Vs, dv, in + (size_t)c0 * a.stride + a.v_off + h * dv, a.stride, len, dv, tid);
+        __syncthreads();
         for (int idx = tid; idx < len * dk; idx += 256) {
             const int t = idx / dk, i = idx - t * dk;
-            const T* tok = in + (size_t)(c0 + t) * a.stride;
-            if (i < half) {
+            if (i < half) {                 // this thread owns the pair (i, i + half) of token t
                 const float ang = (float)(first + (c0 - n0) + t) * a.inv_freq[i];
                 const float c = cosf(ang), sn = sinf(ang);
-                const float qu = to_float(tok[a.q_off + h * dk + i]), qv = to_float(tok[a.q_off + h * dk + i + half]);
-                const float ku = to_float(tok[a.k_off + h * dk + i]), kv = to_float(tok[a.k_off + h * dk + i + half]);
+                const float qu = Qs[t * dk + i], qv = Qs[t * dk + i + half];
+                const float ku = Ks[t * kst + i], kv = Ks[t * kst + i + half];
                 Qs[t * dk + i] = qu * c - qv * sn;
                 Qs[t * dk + i + half] = qv * c + qu * sn;
                 Ks[t * kst + i] = (ku * c - kv * sn) * a.k_scale;
                 Ks[t * kst + i + half] = (kv * c + ku * sn) * a.k_scale;
             } else if (i >= a.rot) {
-                Qs[t * dk + i] = to_float(tok[a.q_off + h * dk + i]);
-                Ks[t * kst + i] = to_float(tok[a.k_off + h * dk + i]) * a.k_scale;
+                Ks[t * kst + i] *= a.k_scale;
             }
-        }
-        for (int idx = tid; idx < len * dv; idx += 256) {
-            const int t = idx / dv, j = idx - t * dv;
-            Vs[t * dv + j] = to_float(in[(size_t)(c0 + t) * a.stride + a.v_off + h * dv + j]);
         }
         __syncthreads();
         // ---- decayed scores A[t][s] = (q_t . k_s) decay^(t-s) for s <= t, zero above the diagonal

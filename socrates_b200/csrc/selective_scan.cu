@@ -43,7 +43,8 @@ struct ScanArgs {
 template <typename T>
 __global__ void __launch_bounds__(THREADS) selective_scan_kernel(ScanArgs a) {
     sb::pdl_launch_dependents();
-    extern __shared__ float bcs[];          // TOKENS * 2 * states
+    extern __shared__ float bcs[];          // TOKENS * 2 * states, then (dt, dt*x, D*x, silu(z)) per channel and token
+    float* tok = bcs + TOKENS * 2 * a.states;
     const int TS = a.TS, states = a.states;
     const int tid = threadIdx.x;
     const int l = tid % TS;
@@ -78,28 +79,42 @@ __global__ void __launch_bounds__(THREADS) selective_scan_kernel(ScanArgs a) {
             bcs[i] = to_float(bc[(size_t)(t0 + t) * a.bc_stride + k]);
         }
         __syncthreads();
-        // the tokens' own values: all loads go out before the first is used (one round trip for the batch)
-        float raws[TOKENS], xvs[TOKENS], zvs[TOKENS];
+        // The tokens' own values, made once per channel: lane l of a channel's group takes the tokens
+        // t = l, l + TS, ... (loads first, all in flight), computes the step size, its product with x and
+        // the output gate, and leaves them in shared memory for the group.
+        {
+            float raws[TOKENS], xv[TOKENS], zv[TOKENS];
 #pragma unroll
-        for (int t = 0; t < TOKENS; ++t) {
-            raws[t] = xvs[t] = zvs[t] = 0.f;
-            if (live && t < nt) {
-                const int n = t0 + t;
-                raws[t] = a.dt_raw[(size_t)n * a.inner + c];
-                xvs[t] = to_float(xs[(size_t)n * a.x_stride + c]);
-                if (l == 0) zvs[t] = to_float(zs[(size_t)n * a.z_stride + c]);
+            for (int k = 0; k < TOKENS; ++k) {
+                const int t = l + k * TS;
+                raws[k] = xv[k] = zv[k] = 0.f;
+                if (live && t < nt) {
+                    const int n = t0 + t;
+                    raws[k] = a.dt_raw[(size_t)n * a.inner + c];
+                    xv[k] = to_float(xs[(size_t)n * a.x_stride + c]);
+                    zv[k] = to_float(zs[(size_t)n * a.z_stride + c]);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < TOKENS; ++k) {
+                const int t = l + k * TS;
+                if (t < nt) {
+                    const float raw = raws[k] + bias;
+                    const float dt = raw > 20.f ? raw : log1pf(expf(raw));
+                    float* o = tok + ((tid / TS) * TOKENS + t) * 4;
+                    o[0] = dt;
+                    o[1] = dt * xv[k];
+                    o[2] = Dc * xv[k];
+                    o[3] = zv[k] / (1.0f + expf(-zv[k]));
+                }
             }
         }
-#pragma unroll
-        for (int t = 0; t < TOKENS; ++t) {
-            if (t >= nt) break;
-            const int n = t0 + t;
-            const float raw = raws[t] + bias;
-            const float dt = live ? (raw > 20.f ? raw : log1pf(expf(raw))) : 0.f;
-            const float xv = xvs[t];
+        __syncwarp();
+        for (int t = 0; t < nt; ++t) {
+            const float4 v = *reinterpret_cast<const float4*>(tok + ((tid / TS) * TOKENS + t) * 4);
+            const float dt = v.x, dx = v.y;
             const float* Bt = bcs + t * 2 * states;
             const float* Ct = Bt + states;
-            const float dx = dt * xv;
             float y = 0.f;
 #pragma unroll
             for (int e = 0; e < NPT; ++e) {
@@ -110,12 +125,9 @@ __global__ void __launch_bounds__(THREADS) selective_scan_kernel(ScanArgs a) {
                 }
             }
             for (int o = TS >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (live && l == 0) {
-                y += Dc * xv;
-                const float zv = zvs[t];
-                ((T*)a.out)[(size_t)n * a.inner + c] = from_float<T>(y * (zv / (1.0f + expf(-zv))));
-            }
+            if (live && l == 0) ((T*)a.out)[(size_t)(t0 + t) * a.inner + c] = from_float<T>((y + v.z) * v.w);
         }
+        __syncwarp();
     }
     if (live) {
 #pragma unroll
@@ -137,16 +149,18 @@ extern "C" int sb_selective_scan(const void* x, long long x_stride, const void* 
                "selective_scan: bad sizes R=%d inner=%d states=%d (at most %d)", R, inner, states, 32 * NPT);
     SB_REQUIRE(R <= 65535, "selective_scan: %d requests exceed one launch", R);
     if (R == 0) return 0;
+    // threads a channel: a power of two, as few as hold the states at NPT each (what a thread does per token
+    // beside its states is the same for every thread of a channel), but four where the states allow it
     int TS = 1;
-    while (TS < 32 && TS * 2 <= states) TS *= 2;          // threads a channel: a power of two, at most the states
     while (TS * NPT < states) TS *= 2;
+    while (TS < 4 && TS * 2 <= states) TS *= 2;
     ScanArgs a;
     a.x = x; a.x_stride = x_stride; a.z = z; a.z_stride = z_stride; a.dt_raw = dt_raw; a.dt_bias = dt_bias;
     a.bc = bc; a.bc_stride = bc_stride; a.A_log = A_log; a.D = D; a.state = state; a.out = out;
     a.seq_starts = seq_starts; a.seq_rows = seq_rows; a.inner = inner; a.states = states; a.TS = TS;
     const int per_block = THREADS / TS;
     dim3 grid((inner + per_block - 1) / per_block, R);
-    const size_t smem = (size_t)TOKENS * 2 * states * sizeof(float);
+    const size_t smem = ((size_t)TOKENS * 2 * states + (size_t)per_block * TOKENS * 4) * sizeof(float);
     if (dtype == SB_F32) sb::launch(selective_scan_kernel<float>, grid, dim3(THREADS), smem, stream, a);
     else if (dtype == SB_BF16) sb::launch(selective_scan_kernel<__nv_bfloat16>, grid, dim3(THREADS), smem, stream, a);
     else SB_REQUIRE(false, "selective_scan: unknown dtype %d", dtype);
