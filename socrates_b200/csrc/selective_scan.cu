@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(THREADS) selective_scan_kernel(ScanArgs a) {
             }
         }
         __syncwarp();
+#pragma unroll 4
         for (int t = 0; t < nt; ++t) {
             const float4 v = *reinterpret_cast<const float4*>(tok + ((tid / TS) * TOKENS + t) * 4);
             const float dt = v.x, dx = v.y;

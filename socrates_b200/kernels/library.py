@@ -52,7 +52,8 @@ _SIGNATURES = {
     "sb_bias_act": [P, P, P, I, LL, P, I, I, I, I, P],
     "sb_short_conv": [P, LL, P, P, P, I, P, I, I, I, P, P, P, I, I, I, P, P, P, P, P, P, P, I, P],
     "sb_short_conv_tail": [P, P, LL, P, I, I, P, P, I, I, P],
-    "sb_retention": [P, LL, I, I, I, I, P, P, P, I, P, P, P, P, I, I, I, I, F, F, I, I, P],
+    "sb_retention": [P, LL, I, I, I, I, P, P, P, P, I, P, P, P, P, I, I, I, I, F, F, I, I, P, LL, I, P],
+    "sb_retention_chunk": [I, I],
     "sb_selective_scan": [P, LL, P, LL, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, P],
     "sb_attention_bias": [P, P, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, I, I, F, F, I, P, P, I, P],
 }

@@ -622,13 +622,18 @@ def short_conv_tail(tail: torch.Tensor, x: torch.Tensor, in_bias: Optional[torch
 def retention(out: torch.Tensor, qkvg: torch.Tensor, offsets: Tuple[int, int, int, int], state: torch.Tensor,
               decay: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, seq_starts: torch.Tensor,
               seq_rows: torch.Tensor, seq_first_pos: torch.Tensor, eps: float, k_scale: float,
-              chunked: bool = False) -> None:
+              chunked: bool = False, inv_freq_lo: Optional[torch.Tensor] = None,
+              scratch: Optional[torch.Tensor] = None) -> None:
     """Decayed linear attention of every request's tokens of the step, in order, through its state slot.
 
     qkvg [N, width] holds q, k (H x dk each), v and g (H x dv each) at the column `offsets`; state float32
     [rows, H, dk, dv] is read and left advanced; out [N, H*dv] = unit_rms(S^T q) * silu(g) per head.
     `chunked`: the kernel for prompt portions, which works on up to 64 tokens of a request at once (the same
-    sums in another order); without it every token is a step of the recurrence, which is what a decode step wants."""
+    sums in another order); without it every token is a step of the recurrence, which is what a decode step wants.
+    `inv_freq_lo`: float32, what rounding to float32 took from each frequency; the angles are then carried in two
+    terms and positions in the thousands cost no accuracy.
+    `scratch` (float32, `retention_scratch_size` elements): lets the chunked kernel give every chunk a block of
+    its own (three launches) when the requests' heads alone would leave the GPU idle."""
     N = qkvg.shape[0]
     _, H, dk, dv = state.shape
     R = seq_rows.numel()
@@ -642,11 +647,23 @@ def retention(out: torch.Tensor, qkvg: torch.Tensor, offsets: Tuple[int, int, in
     _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
     _want(seq_rows, "seq_rows", torch.int32, (R,))
     _want(seq_first_pos, "seq_first_pos", torch.int32, (R,))
+    if inv_freq_lo is not None:
+        _want(inv_freq_lo, "inv_freq_lo", torch.float32, inv_freq.shape)
+    if scratch is not None:
+        _want(scratch, "scratch", torch.float32)
     lib = library()
     check(lib, lib.sb_retention(_ptr(qkvg), qkvg.stride(0), *[int(o) for o in offsets], _ptr(state), _ptr(decay),
-                                _ptr(inv_freq), int(rotary_dim), _ptr(out), _ptr(seq_starts), _ptr(seq_rows),
-                                _ptr(seq_first_pos), R, H, dk, dv, float(eps), float(k_scale), int(chunked),
-                                _code(out.dtype), _stream()), "retention")
+                                _ptr(inv_freq), _ptr(inv_freq_lo), int(rotary_dim), _ptr(out), _ptr(seq_starts), _ptr(seq_rows),
+                                _ptr(seq_first_pos), R, H, dk, dv, float(eps), float(k_scale), int(chunked), N,
+                                _ptr(scratch), scratch.numel() if scratch is not None else 0,
+                                _code(out.dtype), _stream()), "retention", kernels=3 if scratch is not None else 1)
+
+
+def retention_scratch_size(N: int, R: int, H: int, dk: int, dv: int) -> int:
+    """float32 elements of scratch with which `retention(chunked=True)` can spread the chunks of N tokens of R
+    requests over the GPU: one state per chunk and head."""
+    C = int(library().sb_retention_chunk(int(dk), int(dv)))
+    return (-(-N // C) + R) * H * dk * dv if C > 0 else 0
 
 
 def selective_scan(out: torch.Tensor, x: torch.Tensor, z: torch.Tensor, dt_raw: torch.Tensor,

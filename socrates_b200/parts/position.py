@@ -29,6 +29,7 @@ class Rotary(Part):
         if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
         self._table: Optional[torch.Tensor] = None
+        self._low: Optional[torch.Tensor] = None
 
     def inv_freq(self) -> torch.Tensor:
         r = self.rotary_dim
@@ -36,6 +37,17 @@ class Rotary(Part):
             # theta^(-2j/r) in double precision, rounded once to float32
             return (float(self.theta) ** (-torch.arange(0, r, 2, dtype=torch.float64) / r)).float()
         return 1.0 / (self.theta ** (torch.arange(0, r, 2).float() / r))
+
+    def low_table(self, device) -> Optional[torch.Tensor]:
+        """With `table_precision` float64: what rounding to float32 took from each frequency, as float32 (a
+        kernel that carries its angles in two terms adds position * this); None otherwise."""
+        if self.spec.params.get("table_precision") != "float64" or not self.rotary_dim:
+            return None
+        if self._low is None or self._low.device != torch.device(device):
+            r = self.rotary_dim
+            exact = float(self.theta) ** (-torch.arange(0, r, 2, dtype=torch.float64) / r)
+            self._low = (exact - exact.float().double()).float().to(device).contiguous()
+        return self._low
 
     def tables(self, device) -> Tuple[torch.Tensor, int]:
         if self._table is None or self._table.device != torch.device(device):

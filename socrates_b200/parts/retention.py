@@ -68,8 +68,15 @@ class Retention(Part):
         y = ctx.buffers.take("ret_y", N, (H * self.dv,), ctx.dtype)
         inv_freq, rotary_dim = self.position.tables(x.device)
         offsets = (0, H * self.dk, 2 * H * self.dk, 2 * H * self.dk + H * self.dv)
+        scratch = None
+        if not ctx.all_decode and ctx.num_seqs * H < ctx.num_sms:
+            # few requests with long portions: scratch lets every chunk be a block of its own
+            size = ops.retention_scratch_size(N, ctx.num_seqs, H, self.dk, self.dv)
+            if 0 < size <= (1 << 28):
+                scratch = ctx.buffers.take_flat("ret_scratch", size, torch.float32)
         ops.retention(y, qkvg, offsets, cache.state(), self.decay_t, inv_freq, rotary_dim, ctx.seq_starts,
-                      ctx.seq_rows, ctx.seq_first_pos, self.eps, self.key_scale, chunked=not ctx.all_decode)
+                      ctx.seq_rows, ctx.seq_first_pos, self.eps, self.key_scale, chunked=not ctx.all_decode,
+                      inv_freq_lo=getattr(self.position, "low_table", lambda d: None)(x.device), scratch=scratch)
         return Branch(self.o(ctx, y, self.out_buffer, out="partial"))
 
 
