@@ -21,6 +21,7 @@ namespace {
 constexpr int THREADS = 128;
 constexpr int TOKENS = 16;       // tokens whose B and C are staged (and whose dt, x, z are loaded) at once
 constexpr int NPT = 8;           // states per thread at most
+constexpr int SEGMENT = 128;     // tokens per segment of the three-launch form (a multiple of TOKENS)
 
 struct ScanArgs {
     const void* x;           // [N, x_stride] in T, channel c at column c
@@ -38,9 +39,30 @@ struct ScanArgs {
     const int* seq_starts;
     const int* seq_rows;
     int inner, states, TS;
+    int R, seg;              // requests of the step; tokens per segment of the three-launch form
+    float* seg_state;        // [segments of the step, inner, states]
+    float* seg_dt;           // [segments of the step, inner]: the sum of the step sizes in the segment
 };
 
-template <typename T>
+// The segments of a step in one list: request 0's, then request 1's, ...  Finds segment g's request and its
+// number within the request; false if the step has fewer segments.
+__device__ __forceinline__ bool find_segment(int g, const int* seq_starts, int R, int len, int& r, int& si) {
+    for (r = 0; r < R; ++r) {
+        const int ns = (seq_starts[r + 1] - seq_starts[r] + len - 1) / len;
+        if (g < ns) { si = g; return true; }
+        g -= ns;
+    }
+    return false;
+}
+
+// MODE 0: a block walks all tokens of its request (decode steps; many requests).  One long prompt has too
+// few channels to fill the GPU that way (a warp per scheduler, every step's latency exposed), so it runs as
+// three launches over segments of `seg` tokens, each segment a block row of its own:
+// MODE 1: the segment from a zero state: its final state and the sum of its step sizes, to scratch;
+// (selective_scan_join_kernel walks a request's segments: S <- exp(A * sum dt) S + contribution, and leaves
+//  the state BEFORE each segment in scratch and the state after the last in the request's slot;)
+// MODE 2: the segment again from the state before it, this time writing the outputs.
+template <typename T, int MODE>
 __global__ void __launch_bounds__(THREADS) selective_scan_kernel(ScanArgs a) {
     sb::pdl_launch_dependents();
     extern __shared__ float bcs[];          // TOKENS * 2 * states, then (dt, dt*x, D*x, silu(z)) per channel and token
@@ -50,7 +72,7 @@ __global__ void __launch_bounds__(THREADS) selective_scan_kernel(ScanArgs a) {
     const int l = tid % TS;
     const int c = blockIdx.x * (THREADS / TS) + tid / TS;
     const bool live = c < a.inner;
-    const int r = blockIdx.y;
+    int r = blockIdx.y, si = 0;
     float A[NPT], S[NPT];
 #pragma unroll
     for (int e = 0; e < NPT; ++e) {
@@ -60,14 +82,18 @@ __global__ void __launch_bounds__(THREADS) selective_scan_kernel(ScanArgs a) {
     const float bias = live ? a.dt_bias[c] : 0.f;
     const float Dc = live ? a.D[c] : 0.f;
     sb::pdl_wait();
-    const int n0 = a.seq_starts[r], n1 = a.seq_starts[r + 1];
+    if (MODE != 0 && !find_segment(blockIdx.y, a.seq_starts, a.R, a.seg, r, si)) return;
+    const int n0 = MODE == 0 ? a.seq_starts[r] : a.seq_starts[r] + si * a.seg;
+    const int n1 = MODE == 0 ? a.seq_starts[r + 1] : min(a.seq_starts[r + 1], n0 + a.seg);
     const int row = a.seq_rows[r];
-    float* st = a.state + ((size_t)row * a.inner + (live ? c : 0)) * states;
+    float* st = MODE == 0 ? a.state + ((size_t)row * a.inner + (live ? c : 0)) * states
+                          : a.seg_state + ((size_t)blockIdx.y * a.inner + (live ? c : 0)) * states;
 #pragma unroll
     for (int e = 0; e < NPT; ++e) {
         const int n = l + e * TS;
-        S[e] = (live && n < states) ? st[n] : 0.f;
+        S[e] = (MODE != 1 && live && n < states) ? st[n] : 0.f;
     }
+    float dt_sum = 0.f;
     const T* xs = (const T*)a.x;
     const T* zs = (const T*)a.z;
     const T* bc = (const T*)a.bc;
@@ -102,6 +128,7 @@ __global__ void __launch_bounds__(THREADS) selective_scan_kernel(ScanArgs a) {
                     const float raw = raws[k] + bias;
                     const float dt = raw > 20.f ? raw : log1pf(expf(raw));
                     float* o = tok + ((tid / TS) * TOKENS + t) * 4;
+                    dt_sum += dt;
                     o[0] = dt;
                     o[1] = dt * xv[k];
                     o[2] = Dc * xv[k];
@@ -125,12 +152,18 @@ __global__ void __launch_bounds__(THREADS) selective_scan_kernel(ScanArgs a) {
                     y = fmaf(S[e], Ct[k], y);
                 }
             }
-            for (int o = TS >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-            if (live && l == 0) ((T*)a.out)[(size_t)(t0 + t) * a.inner + c] = from_float<T>((y + v.z) * v.w);
+            if (MODE != 1) {
+                for (int o = TS >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+                if (live && l == 0) ((T*)a.out)[(size_t)(t0 + t) * a.inner + c] = from_float<T>((y + v.z) * v.w);
+            }
         }
         __syncwarp();
     }
-    if (live) {
+    if (MODE == 1) {
+        for (int o = TS >> 1; o > 0; o >>= 1) dt_sum += __shfl_xor_sync(0xffffffffu, dt_sum, o);
+        if (live && l == 0) a.seg_dt[(size_t)blockIdx.y * a.inner + c] = dt_sum;
+    }
+    if (live && MODE != 2) {
 #pragma unroll
         for (int e = 0; e < NPT; ++e) {
             const int n = l + e * TS;
@@ -139,13 +172,45 @@ __global__ void __launch_bounds__(THREADS) selective_scan_kernel(ScanArgs a) {
     }
 }
 
+// Between MODE 1 and MODE 2: one thread per (channel, state) of a request walks its segments.
+__global__ void __launch_bounds__(256) selective_scan_join_kernel(ScanArgs a) {
+    sb::pdl_launch_dependents();
+    const int i = blockIdx.x * 256 + threadIdx.x, r = blockIdx.y;
+    const int size = a.inner * a.states;
+    const float A = i < size ? -expf(a.A_log[i]) : 0.f;
+    sb::pdl_wait();
+    if (i >= size) return;
+    int base = 0;
+    for (int q = 0; q < r; ++q) base += (a.seq_starts[q + 1] - a.seq_starts[q] + a.seg - 1) / a.seg;
+    const int ns = (a.seq_starts[r + 1] - a.seq_starts[r] + a.seg - 1) / a.seg;
+    const int c = i / a.states;
+    float* slot = a.state + (size_t)a.seq_rows[r] * size + i;
+    float s = *slot;
+    for (int g0 = 0; g0 < ns; g0 += 8) {                         // eight segments' loads in flight
+        float u[8], d[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (g0 + k < ns) {
+                u[k] = a.seg_state[(size_t)(base + g0 + k) * size + i];
+                d[k] = a.seg_dt[(size_t)(base + g0 + k) * a.inner + c];
+            }
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (g0 + k < ns) {
+                a.seg_state[(size_t)(base + g0 + k) * size + i] = s;
+                s = fmaf(expf(A * d[k]), s, u[k]);
+            }
+    }
+    *slot = s;
+}
+
 }  // namespace
 
 extern "C" int sb_selective_scan(const void* x, long long x_stride, const void* z, long long z_stride,
                                  const float* dt_raw, const float* dt_bias, const void* bc, long long bc_stride,
                                  const float* A_log, const float* D, float* state, void* out,
-                                 const int* seq_starts, const int* seq_rows, int R, int inner, int states,
-                                 int dtype, cudaStream_t stream) {
+                                 const int* seq_starts, const int* seq_rows, int R, int inner, int states, int N,
+                                 float* scratch, long long scratch_floats, int dtype, cudaStream_t stream) {
     SB_REQUIRE(R >= 0 && inner > 0 && states > 0 && states <= 32 * NPT,
                "selective_scan: bad sizes R=%d inner=%d states=%d (at most %d)", R, inner, states, 32 * NPT);
     SB_REQUIRE(R <= 65535, "selective_scan: %d requests exceed one launch", R);
@@ -162,8 +227,31 @@ extern "C" int sb_selective_scan(const void* x, long long x_stride, const void* 
     const int per_block = THREADS / TS;
     dim3 grid((inner + per_block - 1) / per_block, R);
     const size_t smem = ((size_t)TOKENS * 2 * states + (size_t)per_block * TOKENS * 4) * sizeof(float);
-    if (dtype == SB_F32) sb::launch(selective_scan_kernel<float>, grid, dim3(THREADS), smem, stream, a);
-    else if (dtype == SB_BF16) sb::launch(selective_scan_kernel<__nv_bfloat16>, grid, dim3(THREADS), smem, stream, a);
-    else SB_REQUIRE(false, "selective_scan: unknown dtype %d", dtype);
+    SB_REQUIRE(dtype == SB_F32 || dtype == SB_BF16, "selective_scan: unknown dtype %d", dtype);
+    // few requests with long portions: segments in parallel (three launches) if the caller lent scratch
+    const int segs = (N + SEGMENT - 1) / SEGMENT + R;
+    const bool spread = scratch != nullptr && (int)grid.x * R < 4 * 148 && segs > 2 * R &&
+                        (long long)segs * inner * (states + 1) <= scratch_floats;
+    a.R = R; a.seg = SEGMENT; a.seg_state = scratch; a.seg_dt = scratch ? scratch + (size_t)segs * inner * states : nullptr;
+    if (!spread) {
+        if (dtype == SB_F32) sb::launch(selective_scan_kernel<float, 0>, grid, dim3(THREADS), smem, stream, a);
+        else sb::launch(selective_scan_kernel<__nv_bfloat16, 0>, grid, dim3(THREADS), smem, stream, a);
+        SB_LAUNCH_CHECK();
+    }
+    dim3 sgrid(grid.x, segs), jgrid((inner * states + 255) / 256, R);
+    if (dtype == SB_F32) {
+        sb::launch(selective_scan_kernel<float, 1>, sgrid, dim3(THREADS), smem, stream, a);
+        sb::launch(selective_scan_join_kernel, jgrid, dim3(256), 0, stream, a);
+        sb::launch(selective_scan_kernel<float, 2>, sgrid, dim3(THREADS), smem, stream, a);
+    } else {
+        sb::launch(selective_scan_kernel<__nv_bfloat16, 1>, sgrid, dim3(THREADS), smem, stream, a);
+        sb::launch(selective_scan_join_kernel, jgrid, dim3(256), 0, stream, a);
+        sb::launch(selective_scan_kernel<__nv_bfloat16, 2>, sgrid, dim3(THREADS), smem, stream, a);
+    }
     SB_LAUNCH_CHECK();
+}
+
+// float32 elements of scratch with which a step of N tokens of R requests can run its segments in parallel.
+extern "C" long long sb_selective_scan_scratch(int N, int R, int inner, int states) {
+    return (long long)((N + SEGMENT - 1) / SEGMENT + R) * inner * (states + 1);
 }

@@ -54,7 +54,7 @@ _SIGNATURES = {
     "sb_short_conv_tail": [P, P, LL, P, I, I, P, P, I, I, P],
     "sb_retention": [P, LL, I, I, I, I, P, P, P, P, I, P, P, P, P, I, I, I, I, F, F, I, I, P, LL, I, P],
     "sb_retention_chunk": [I, I],
-    "sb_selective_scan": [P, LL, P, LL, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, P],
+    "sb_selective_scan": [P, LL, P, LL, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, P, LL, I, P],
     "sb_attention_bias": [P, P, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, I, I, F, F, I, P, P, I, P],
 }
 
@@ -64,6 +64,9 @@ def declare(lib: ctypes.CDLL, signatures: dict) -> None:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
+    if hasattr(lib, "sb_selective_scan_scratch"):
+        lib.sb_selective_scan_scratch.argtypes = [c_int, c_int, c_int, c_int]
+        lib.sb_selective_scan_scratch.restype = c_longlong
     lib.sb_last_error.argtypes = []
     lib.sb_last_error.restype = c_char_p
 

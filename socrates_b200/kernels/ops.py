@@ -668,11 +668,14 @@ def retention_scratch_size(N: int, R: int, H: int, dk: int, dv: int) -> int:
 
 def selective_scan(out: torch.Tensor, x: torch.Tensor, z: torch.Tensor, dt_raw: torch.Tensor,
                    dt_bias: torch.Tensor, bc: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor,
-                   state: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor) -> None:
+                   state: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor,
+                   scratch: Optional[torch.Tensor] = None) -> None:
     """Selective scan of every request's tokens of the step, in order, through its state slot.
 
     x, z [N, inner] (row strides may exceed inner), bc [N, 2*states] (B then C) in out's dtype; dt_raw float32
-    [N, inner] before bias and softplus; A_log float32 [inner, states]; state float32 [rows, inner, states]."""
+    [N, inner] before bias and softplus; A_log float32 [inner, states]; state float32 [rows, inner, states].
+    `scratch` (float32, `selective_scan_scratch_size` elements): lets few requests with long portions run as
+    segments of 128 tokens in parallel (three launches: the same sums with the decays of a segment multiplied up)."""
     N, inner = out.shape
     states = A_log.shape[1]
     R = seq_rows.numel()
@@ -689,11 +692,19 @@ def selective_scan(out: torch.Tensor, x: torch.Tensor, z: torch.Tensor, dt_raw: 
         raise KernelError(f"state must be [rows, {inner}, {states}], got {tuple(state.shape)}")
     _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
     _want(seq_rows, "seq_rows", torch.int32, (R,))
+    if scratch is not None:
+        _want(scratch, "scratch", torch.float32)
     lib = library()
     check(lib, lib.sb_selective_scan(_ptr(x), x.stride(0), _ptr(z), z.stride(0), _ptr(dt_raw), _ptr(dt_bias),
                                      _ptr(bc), bc.stride(0), _ptr(A_log), _ptr(D), _ptr(state), _ptr(out),
-                                     _ptr(seq_starts), _ptr(seq_rows), R, inner, states, _code(out.dtype),
-                                     _stream()), "selective_scan")
+                                     _ptr(seq_starts), _ptr(seq_rows), R, inner, states, N, _ptr(scratch),
+                                     scratch.numel() if scratch is not None else 0, _code(out.dtype),
+                                     _stream()), "selective_scan", kernels=3 if scratch is not None else 1)
+
+
+def selective_scan_scratch_size(N: int, R: int, inner: int, states: int) -> int:
+    """float32 elements of scratch for `selective_scan(..., scratch=...)` on N tokens of R requests."""
+    return int(library().sb_selective_scan_scratch(int(N), int(R), int(inner), int(states)))
 
 
 def attention_bias(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,

@@ -84,8 +84,14 @@ class SelectiveScan(Part):
         bc = self.w_bc(ctx, xc, "ss_bc")
         dt_raw = self.w_dt(ctx, dt_in, "ss_dt", out="float32")
         y = ctx.buffers.take("ss_y", N, (I,), ctx.dtype)
+        scratch = None
+        if not ctx.all_decode and N > 128 * ctx.num_seqs:
+            # few requests with long portions: scratch lets the kernel run segments of the prompt in parallel
+            size = ops.selective_scan_scratch_size(N, ctx.num_seqs, I, self.states)
+            if size <= (1 << 28):
+                scratch = ctx.buffers.take_flat("ss_scratch", size, torch.float32)
         ops.selective_scan(y, xc, xz[:, I:], dt_raw, self.dt_bias, bc, self.A_log, self.D, cache.state("ssm"),
-                           ctx.seq_starts, ctx.seq_rows)
+                           ctx.seq_starts, ctx.seq_rows, scratch=scratch)
         return Branch(self.o(ctx, y, self.out_buffer, out="partial"))
 
 

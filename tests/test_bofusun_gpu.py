@@ -136,7 +136,7 @@ def mixer_in_portions(tmp_path, name, dtype, entry, sizes, n, plain_fn):
     from socrates_b200.engine.context import CacheView
     from socrates_b200.engine.runner import StepEntry
     folder, cfg, w = make_folder(tmp_path, name)
-    h = Harness(folder, dtype, max_len=256)
+    h = Harness(folder, dtype, max_len=640)
     layer = h.model.plan.order[entry].layer
     mixer = h.model.layers[layer].mixer
     g = torch.Generator().manual_seed(entry + n)
@@ -176,6 +176,18 @@ def test_parallel_part(tmp_path, dtype, sizes, name, entry):
     edge and several page borders, in one portion, token by token and in ragged portions."""
     err = mixer_in_portions(tmp_path, name, dtype, entry, sizes, 90, plain.parallel_mixer)
     assert err < PART_TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("sizes", [(600,), (290, 1, 309), (64, 2, 400, 134)])
+@pytest.mark.parametrize("name,entry", [("P", 0), ("P", 1), ("R", 2)])
+def test_long_portions(tmp_path, dtype, sizes, name, entry):
+    """Portions of hundreds of tokens: retention in chunks and the scan in segments that run side by side
+    (scratch states, a scan over them), attention far past its window, against the same plain functions."""
+    layer_type = TINY[name][0]["layers"][{0: 0, 1: 1, 2: 2}[entry] if name == "P" else 2]["type"]
+    fn = plain.retention if layer_type == "retention" else plain.parallel_mixer
+    err = mixer_in_portions(tmp_path, name, dtype, entry, sizes, 600, fn)
+    assert err < PART_TOL[dtype] * 2
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
