@@ -188,6 +188,169 @@ __global__ void __launch_bounds__(THREADS) bias_attention_kernel(BiasAttnArgs a)
     }
 }
 
+
+// ----------------------------------------------------------------------------------------
+// The same attention for prompt portions, a tile of consecutive tokens of one request per block.
+// A tile's queries see almost the same keys, so a key or value row fetched once serves all of them:
+// 64 rows (queries x the query heads of a pass) share every 128-key chunk.
+//   scores: thread t owns key t of the chunk, keeps 64 dot products in registers and reads its key row
+//           in 16-byte pieces; q comes from shared memory four dims a load;
+//   softmax: a warp per row, running maximum and sum as in the kernel above;
+//   values: thread t owns value dim t and 64 partial outputs; weights come from shared memory four keys a load.
+// Scores, weights and sums are float32.  Dv <= 128 and 16-byte key rows; other shapes use the kernel above.
+constexpr int ROWS = 64;
+
+struct TileArgs {
+    BiasAttnArgs b;
+    const int* seq_starts;
+    const int* seq_rows;
+    const int* seq_first_pos;
+    int R, QT, GP;             // requests; queries per tile and heads per pass (QT * GP = ROWS)
+};
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS) bias_attention_tile_kernel(TileArgs ta) {
+    sb::pdl_launch_dependents();
+    const BiasAttnArgs& a = ta.b;
+    extern __shared__ float tsm[];
+    const int Dk = a.Dk, Dv = a.Dv, BS = a.BS, QT = ta.QT, GP = ta.GP;
+    float* Qs = tsm;                        // [ROWS][Dk]
+    float* Ps = Qs + ROWS * Dk;             // [ROWS][KEYS]
+    __shared__ float run_max[ROWS], run_sum[ROWS], rescale[ROWS];
+    __shared__ int pg[KEYS];
+    const int kh = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = a.Hq / a.Hkv;
+    sb::pdl_wait();
+    // which request and which of its tiles
+    int r = 0, ti = blockIdx.y;
+    for (; r < ta.R; ++r) {
+        const int nt = (ta.seq_starts[r + 1] - ta.seq_starts[r] + QT - 1) / QT;
+        if (ti < nt) break;
+        ti -= nt;
+    }
+    if (r == ta.R) return;
+    const int n_first = ta.seq_starts[r] + ti * QT;
+    const int nq = min(QT, ta.seq_starts[r + 1] - n_first);                 // queries in this tile
+    const int pos_first = ta.seq_first_pos[r] + ti * QT, pos_last = pos_first + nq - 1;
+    const int lo_tile = (a.window > 0 && pos_first + 1 > a.window) ? pos_first + 1 - a.window : 0;
+    const int* table = a.block_table + (size_t)ta.seq_rows[r] * a.table_width;
+    const T* q = (const T*)a.q;
+    const T* kp = (const T*)a.k_pool;
+    const T* vp = (const T*)a.v_pool;
+    constexpr int VEC = Vec16<T>::N;
+
+    for (int g0 = 0; g0 < G; g0 += GP) {
+        const int gn = min(GP, G - g0), h0 = kh * G + g0;
+        __syncthreads();
+        // row = query * GP + head of the pass; rows past the tile's queries or the pass's heads stay zero
+        for (int i = tid; i < ROWS * Dk; i += THREADS) {
+            const int row = i / Dk, d = i - row * Dk, qi = row / GP, g = row - qi * GP;
+            Qs[i] = (qi < nq && g < gn) ? to_float(q[((size_t)(n_first + qi) * a.Hq + h0 + g) * Dk + d]) : 0.f;
+        }
+        if (tid < ROWS) { run_max[tid] = -INFINITY; run_sum[tid] = 0.f; rescale[tid] = 0.f; }
+        float acc[ROWS];
+#pragma unroll
+        for (int row = 0; row < ROWS; ++row) acc[row] = 0.f;
+        __syncthreads();
+        for (int c0 = lo_tile; c0 <= pos_last; c0 += KEYS) {
+            // ---- scores of this thread's key against all rows
+            {
+                const int key = c0 + tid;
+                const bool have = key <= pos_last;
+                float dot[ROWS];
+#pragma unroll
+                for (int row = 0; row < ROWS; ++row) dot[row] = 0.f;
+                if (have) {
+                    const int page = table[key / BS];
+                    pg[tid] = page;
+                    const T* kr = kp + (((size_t)page * a.Hkv + kh) * BS + key % BS) * Dk;
+                    for (int d = 0; d < Dk; d += VEC) {
+                        Vec16<T> kv;
+                        kv.load(kr + d);
+#pragma unroll
+                        for (int e = 0; e < VEC; e += 4) {
+                            const float k0 = kv.get(e), k1 = kv.get(e + 1), k2 = kv.get(e + 2), k3 = kv.get(e + 3);
+#pragma unroll
+                            for (int row = 0; row < ROWS; ++row) {
+                                const float4 qv = *reinterpret_cast<const float4*>(Qs + row * Dk + d + e);
+                                dot[row] = fmaf(qv.x, k0, fmaf(qv.y, k1, fmaf(qv.z, k2, fmaf(qv.w, k3, dot[row]))));
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int row = 0; row < ROWS; ++row) {
+                    const int qi = row / GP, g = row - qi * GP;
+                    const int pos = pos_first + qi;
+                    const int lo = (a.window > 0 && pos + 1 > a.window) ? pos + 1 - a.window : 0;
+                    float sc = -INFINITY;
+                    if (have && qi < nq && g < gn && key >= lo && key <= pos) {
+                        sc = dot[row] * a.scale;
+                        if (a.cap > 0.f) sc = a.cap * tanhf(sc / a.cap);
+                        if (a.dist_bias) sc += a.dist_bias[(size_t)(h0 + g) * a.L + min(pos - key, a.L - 1)];
+                    }
+                    Ps[row * KEYS + tid] = sc;
+                }
+            }
+            __syncthreads();
+            // ---- running maximum and weights, a warp per row
+            for (int row = warp; row < ROWS; row += THREADS / 32) {
+                float* pr = Ps + row * KEYS;
+                float mx = -INFINITY;
+                for (int t = lane; t < KEYS; t += 32) mx = fmaxf(mx, pr[t]);
+                mx = warp_max(mx);
+                const float m_old = run_max[row], m_new = fmaxf(m_old, mx);
+                const float base = m_new == -INFINITY ? 0.f : m_new;      // a row that has seen no key yet
+                float sum = 0.f;
+                for (int t = lane; t < KEYS; t += 32) {
+                    const float p = expf(pr[t] - base);
+                    pr[t] = p;
+                    sum += p;
+                }
+                sum = warp_sum(sum);
+                if (lane == 0) {
+                    const float f = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+                    rescale[row] = f;
+                    run_sum[row] = run_sum[row] * f + sum;
+                    run_max[row] = m_new;
+                }
+            }
+            __syncthreads();
+            // ---- weighted values: this thread's value dim, four keys a step
+#pragma unroll
+            for (int row = 0; row < ROWS; ++row) acc[row] *= rescale[row];
+            const int nk = min(KEYS, pos_last + 1 - c0);
+            for (int t = 0; t < nk; t += 4) {
+                float v[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int key = c0 + t + j;
+                    v[j] = (t + j < nk && tid < Dv)
+                               ? to_float(vp[(((size_t)pg[t + j] * a.Hkv + kh) * BS + key % BS) * Dv + tid]) : 0.f;
+                }
+#pragma unroll
+                for (int row = 0; row < ROWS; ++row) {
+                    const float4 w = *reinterpret_cast<const float4*>(Ps + row * KEYS + t);
+                    acc[row] = fmaf(w.x, v[0], fmaf(w.y, v[1], fmaf(w.z, v[2], fmaf(w.w, v[3], acc[row]))));
+                }
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int row = 0; row < ROWS; ++row) {
+            const int qi = row / GP, g = row - qi * GP;
+            if (qi >= nq || g >= gn || tid >= Dv) continue;
+            const int h = h0 + g, n = n_first + qi;
+            float f = 1.0f / run_sum[row];
+            if (a.gate) {
+                const float z = to_float(((const T*)a.gate)[(size_t)n * a.gate_stride + h]);
+                f *= 1.0f / (1.0f + expf(-z));
+            }
+            ((T*)a.out)[((size_t)n * a.Hq + h) * Dv + tid] = from_float<T>(acc[row] * f);
+        }
+    }
+}
+
 }  // namespace
 
 extern "C" int sb_attention_bias(void* out, const void* q, const void* k_pool, const void* v_pool,
@@ -228,6 +391,57 @@ extern "C" int sb_attention_bias(void* out, const void* q, const void* k_pool, c
                        (const float*)part_o, (const float*)part_ml, Hq, Dv, num_partitions);
     } else {
         SB_REQUIRE(false, "attention_bias: unknown dtype %d", dtype);
+    }
+    SB_LAUNCH_CHECK();
+}
+
+// Prompt portions: a tile of consecutive tokens of a request per block (see bias_attention_tile_kernel).
+// Returns SB_ERR_ARG for shapes the tile kernel does not take; `sb_attention_bias_tile_supports` says which.
+extern "C" int sb_attention_bias_tile_supports(int Hq, int Hkv, int Dk, int Dv, int dtype) {
+    const int vec = dtype == SB_BF16 ? 8 : 4;
+    return Hq % Hkv == 0 && Dk % vec == 0 && Dk >= vec && Dk <= 256 && Dv >= 1 && Dv <= THREADS;
+}
+
+extern "C" int sb_attention_bias_tile(void* out, const void* q, const void* k_pool, const void* v_pool,
+                                      const int* block_table, int table_width, const int* seq_starts,
+                                      const int* seq_rows, const int* seq_first_pos, int R, const void* gate,
+                                      long long gate_stride, const float* dist_bias, int L, int N, int Hq, int Hkv,
+                                      int Dk, int Dv, int page_size, int window, float scale, float cap, int dtype,
+                                      cudaStream_t stream) {
+    SB_REQUIRE(sb_attention_bias_tile_supports(Hq, Hkv, Dk, Dv, dtype),
+               "attention_bias_tile: heads %d/%d of %d (keys) and %d (values) are not served", Hq, Hkv, Dk, Dv);
+    SB_REQUIRE((reinterpret_cast<uintptr_t>(k_pool) & 15) == 0, "attention_bias_tile: the key pool must be 16-byte aligned");
+    SB_REQUIRE(page_size > 0 && table_width > 0 && window >= 0 && R >= 0, "attention_bias_tile: bad sizes");
+    SB_REQUIRE(dist_bias == nullptr || L >= 1, "attention_bias_tile: a bias table needs a length");
+    if (N == 0 || R == 0) return 0;
+    const int G = Hq / Hkv;
+    TileArgs ta;
+    BiasAttnArgs& a = ta.b;
+    a.out = out; a.q = q; a.k_pool = k_pool; a.v_pool = v_pool; a.block_table = block_table;
+    a.table_width = table_width; a.token_rows = nullptr; a.positions = nullptr; a.gate = gate;
+    a.gate_stride = gate_stride; a.dist_bias = dist_bias; a.L = L > 0 ? L : 1; a.Hq = Hq; a.Hkv = Hkv; a.Dk = Dk;
+    a.Dv = Dv; a.BS = page_size; a.window = window; a.scale = scale; a.cap = cap; a.NP = 1; a.part_o = nullptr;
+    a.part_ml = nullptr;
+    ta.seq_starts = seq_starts; ta.seq_rows = seq_rows; ta.seq_first_pos = seq_first_pos; ta.R = R;
+    ta.GP = G >= 4 ? 4 : (G >= 2 ? 2 : 1);
+    ta.QT = ROWS / ta.GP;
+    const int tiles = (N + ta.QT - 1) / ta.QT + R;
+    SB_REQUIRE(tiles <= 65535, "attention_bias_tile: %d tiles exceed one launch", tiles);
+    const size_t smem = (size_t)ROWS * (Dk + KEYS) * sizeof(float);
+    dim3 grid(Hkv, tiles);
+    static sb::OncePerDevice once_f, once_b;
+    if (dtype == SB_F32) {
+        if (!once_f.flag()) {
+            cudaFuncSetAttribute(bias_attention_tile_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            once_f.flag() = true;
+        }
+        sb::launch(bias_attention_tile_kernel<float>, grid, dim3(THREADS), smem, stream, ta);
+    } else {
+        if (!once_b.flag()) {
+            cudaFuncSetAttribute(bias_attention_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            once_b.flag() = true;
+        }
+        sb::launch(bias_attention_tile_kernel<__nv_bfloat16>, grid, dim3(THREADS), smem, stream, ta);
     }
     SB_LAUNCH_CHECK();
 }

@@ -55,6 +55,8 @@ _SIGNATURES = {
     "sb_retention": [P, LL, I, I, I, I, P, P, P, P, I, P, P, P, P, I, I, I, I, F, F, I, I, P, LL, I, P],
     "sb_retention_chunk": [I, I],
     "sb_selective_scan": [P, LL, P, LL, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, P, LL, I, P],
+    "sb_attention_bias_tile_supports": [I, I, I, I, I],
+    "sb_attention_bias_tile": [P, P, P, P, P, I, P, P, P, I, P, LL, P, I, I, I, I, I, I, I, I, F, F, I, P],
     "sb_attention_bias": [P, P, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, I, I, F, F, I, P, P, I, P],
 }
 

@@ -753,3 +753,50 @@ def attention_bias(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_p
                                      float(softcap), int(num_partitions), _ptr(part_o), _ptr(part_ml),
                                      _code(q.dtype), _stream()), "attention_bias",
           kernels=2 if num_partitions > 1 else 1)
+
+
+def attention_bias_tile_supports(num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
+                                 dtype: torch.dtype) -> bool:
+    """Whether the tile kernel for prompt portions takes this shape (value heads up to 128 dims, key rows
+    that are whole 16-byte pieces)."""
+    return bool(library().sb_attention_bias_tile_supports(num_heads, num_kv_heads, key_dim, value_dim, _code(dtype)))
+
+
+def attention_bias_tile(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                        block_table: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor,
+                        seq_first_pos: torch.Tensor, num_heads: int, scale: float, window: int = 0,
+                        softcap: float = 0.0, dist_bias: Optional[torch.Tensor] = None,
+                        gate: Optional[torch.Tensor] = None) -> None:
+    """`attention_bias` for prompt portions: request r brings tokens seq_starts[r] .. seq_starts[r+1]-1 at
+    positions seq_first_pos[r], +1, ... of cache row seq_rows[r]; a block serves a tile of consecutive tokens
+    of one request, so a key or value row fetched once serves all of them.  The same arithmetic in float32."""
+    N = q.shape[0]
+    pages, Hkv, BS, Dk = k_pool.shape
+    Dv = v_pool.shape[3]
+    Hq = num_heads
+    R = seq_rows.numel()
+    _want(q, "q", k_pool.dtype, (N, Hq * Dk))
+    _want(out, "out", q.dtype, (N, Hq * Dv))
+    _want(k_pool, "k_pool")
+    _want(v_pool, "v_pool", k_pool.dtype, (pages, Hkv, BS, Dv))
+    _want(block_table, "block_table", torch.int32)
+    _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
+    _want(seq_rows, "seq_rows", torch.int32, (R,))
+    _want(seq_first_pos, "seq_first_pos", torch.int32, (R,))
+    L = 0
+    if dist_bias is not None:
+        _want(dist_bias, "dist_bias", torch.float32)
+        if dist_bias.dim() != 2 or dist_bias.shape[0] != Hq:
+            raise KernelError(f"dist_bias must be [{Hq}, L], got {tuple(dist_bias.shape)}")
+        L = dist_bias.shape[1]
+    gate_stride = 0
+    if gate is not None:
+        if gate.dtype != q.dtype or gate.dim() != 2 or gate.shape[0] != N or gate.shape[1] < Hq or gate.stride(1) != 1:
+            raise KernelError(f"gate must be [{N}, >= {Hq}] in {q.dtype} with unit column stride")
+        gate_stride = gate.stride(0)
+    lib = library()
+    check(lib, lib.sb_attention_bias_tile(_ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+                                          block_table.shape[1], _ptr(seq_starts), _ptr(seq_rows), _ptr(seq_first_pos),
+                                          R, _ptr(gate), gate_stride, _ptr(dist_bias), L, N, Hq, Hkv, Dk, Dv, BS,
+                                          int(window), float(scale), float(softcap), _code(q.dtype), _stream()),
+          "attention_bias_tile")

@@ -123,12 +123,19 @@ class WindowBiasAttention(Part):
         if tail is not None:
             ops.short_conv_tail(tail, qkvg, self.in_bias, self.taps, ctx.seq_starts, ctx.seq_rows)
         attn = ctx.buffers.take("wa_attn", N, (self.H * self.dv,), ctx.dtype)
+        gate = qkvg[:, self.C:self.C + self.H]
+        if (not ctx.all_decode and N >= 4 * ctx.num_seqs
+                and ops.attention_bias_tile_supports(self.H, self.G, self.dk, self.dv, ctx.dtype)):
+            # prompt portions: a tile of a request's consecutive tokens per block shares the keys it reads
+            ops.attention_bias_tile(attn, q, k_pool, v_pool, table, ctx.seq_starts, ctx.seq_rows, ctx.seq_first_pos,
+                                    self.H, self.scale, self.window or 0, self.softcap, self.dist_bias, gate=gate)
+            return Branch(self.o(ctx, attn, self.out_buffer, out="partial"))
         NP, part_o, part_ml = self.partitions(ctx, N, cache.manager.max_len), None, None
         if NP > 1:
             part_o = ctx.buffers.take_flat("attn_part_o", N * self.H * NP * self.dv, torch.float32)
             part_ml = ctx.buffers.take_flat("attn_part_ml", N * self.H * NP * 2, torch.float32)
         ops.attention_bias(attn, q, k_pool, v_pool, table, ctx.token_rows, ctx.positions, self.H, self.scale,
-                           self.window or 0, self.softcap, self.dist_bias, gate=qkvg[:, self.C:self.C + self.H],
+                           self.window or 0, self.softcap, self.dist_bias, gate=gate,
                            num_partitions=NP, part_o=part_o, part_ml=part_ml)
         return Branch(self.o(ctx, attn, self.out_buffer, out="partial"))
 
