@@ -192,13 +192,13 @@ __global__ void __launch_bounds__(THREADS) bias_attention_kernel(BiasAttnArgs a)
 // ----------------------------------------------------------------------------------------
 // The same attention for prompt portions, a tile of consecutive tokens of one request per block.
 // A tile's queries see almost the same keys, so a key or value row fetched once serves all of them:
-// 64 rows (queries x the query heads of a pass) share every 128-key chunk.
-//   scores: thread t owns key t of the chunk, keeps 64 dot products in registers and reads its key row
+// 32 rows (queries x the query heads of a pass) share every 128-key chunk.
+//   scores: thread t owns key t of the chunk, keeps 32 dot products in registers and reads its key row
 //           in 16-byte pieces; q comes from shared memory four dims a load;
 //   softmax: a warp per row, running maximum and sum as in the kernel above;
-//   values: thread t owns value dim t and 64 partial outputs; weights come from shared memory four keys a load.
+//   values: thread t owns value dim t and 32 partial outputs; weights come from shared memory four keys a load.
 // Scores, weights and sums are float32.  Dv <= 128 and 16-byte key rows; other shapes use the kernel above.
-constexpr int ROWS = 64;
+constexpr int ROWS = 32;       // 64 rows need 255 registers a thread (two blocks of four warps an SM); 32 leave room for three
 
 struct TileArgs {
     BiasAttnArgs b;
@@ -209,7 +209,7 @@ struct TileArgs {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(THREADS) bias_attention_tile_kernel(TileArgs ta) {
+__global__ void __launch_bounds__(THREADS, 3) bias_attention_tile_kernel(TileArgs ta) {
     sb::pdl_launch_dependents();
     const BiasAttnArgs& a = ta.b;
     extern __shared__ float tsm[];
