@@ -491,3 +491,27 @@ def test_replay_program(models, tmp_path, dtype):
     result = run_trace(folder, dtype, trace, trace.most_held, tmp_path / "out")
     worst, where = compare(trace, result, reference, key=lambda rid: rid.split(":")[1])
     assert worst < TOL[torch.float32 if dtype == "float32" else torch.bfloat16], where
+
+
+def test_command_line(models, tmp_path):
+    """The generation command line on a Bofusun folder, and on a bare config.json with random weights
+    (which also draws the distance table with its default length)."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    folder, cfg, _, _, _ = models["P"]
+    common = ["--max-new-tokens", "7", "--max-len", "96", "--max-batch", "2"]
+    proc = subprocess.run([sys.executable, "-m", "socrates_b200.inference_paged", "--model", str(folder),
+                           "--num-prompts", "3", "--prompt-len", "21", "--prompt", "hello", *common],
+                          cwd=str(root), capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert "4 requests, 2 rows" in proc.stdout and "> hello" in proc.stdout
+    path = tmp_path / "config.json"
+    path.write_text(json.dumps(TINY["R"][0]))
+    proc = subprocess.run([sys.executable, "-m", "socrates_b200.inference_paged", "--random-config", str(path),
+                           "--num-prompts", "2", "--prompt-len", "30", "--dtype", "float32", *common],
+                          cwd=str(root), capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert "2 requests, 2 rows" in proc.stdout and "tok/s" in proc.stdout.splitlines()[-1]
