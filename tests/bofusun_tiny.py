@@ -52,6 +52,12 @@ TINY = {
                {"type": "parallel", "mixer": _par(2, 1, 16, 16, 4, 0.2, 3.0, 48, 50, 16, 4, 1, 1),
                 "mlp": {"kind": "dense", "ff": 56}}],
            "loop": {"start": 1, "stop": 2, "times": 1}}, 20),
+    # retention only (no pages at all), a feed-forward on every layer, the whole model run twice
+    "S": ({"architecture": "Bofusun", "vocab": 300, "width": 24, "norm": {"eps": 1e-5},
+           "layers": [
+               {"type": "retention", "mixer": _ret(2, 4, 12, 2, 50.0, [0.9, 0.99]), "mlp": {"kind": "dense", "ff": 16}},
+               {"type": "retention", "mixer": _ret(1, 24, 24, 24, 1e6, [0.97]), "mlp": {"kind": "dense", "ff": 32}}],
+           "loop": {"start": 0, "stop": 2, "times": 2}}, 4),
 }
 
 

@@ -265,7 +265,7 @@ def models(tmp_path_factory):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
 def test_whole_prompts_decoding_and_portions(models, dtype, name):
     folder, cfg, w, seqs, want = models[name]
     h = Harness(folder, dtype)
@@ -286,7 +286,7 @@ def test_whole_prompts_decoding_and_portions(models, dtype, name):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["P", "R"])
+@pytest.mark.parametrize("name", ["P", "R", "S"])
 def test_unequal_requests_in_one_batch(models, dtype, name):
     """Four requests of 150, 23, 77 and 4 tokens: portions of some beside single tokens of others, a
     request that joins late and one that sits steps out; each must come out as it does alone."""
@@ -449,7 +449,7 @@ def test_one_key_at_the_windows_edge_decides(tmp_path, dtype):
 # the entry point, the scheduler, the command-line replay
 
 @pytest.mark.parametrize("dtype,graphs", [("float32", False), ("bfloat16", True)])
-@pytest.mark.parametrize("name", ["P", "R"])
+@pytest.mark.parametrize("name", ["P", "R", "S"])
 def test_greedy_generation_through_the_entry_point(models, name, dtype, graphs):
     """Five requests through Engine: queued, admitted as rows come free, prompts cut by the token
     budget, decoded side by side (bfloat16: through recorded graphs), 90 new tokens each, which passes
