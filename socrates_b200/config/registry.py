@@ -12,6 +12,7 @@ from pathlib import Path
 from typing import Any, Dict, Mapping
 
 from .bofusun import BofusunConfig
+from .loletar import LoletarConfig
 from .qwen3 import ConfigError, Qwen3Config
 
 _ARCHITECTURES: Dict[str, Any] = {}
@@ -57,3 +58,4 @@ def load_config(model_dir: str | Path):
 
 register_architecture(Qwen3Config.architecture, Qwen3Config)
 register_architecture(BofusunConfig.architecture, BofusunConfig)
+register_architecture(LoletarConfig.architecture, LoletarConfig)

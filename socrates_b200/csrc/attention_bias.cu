@@ -6,7 +6,8 @@
 //   s_ij = cap * tanh(s_ij / cap)                  (cap > 0)
 //   s_ij += dist_bias[h][min(i - j, L - 1)]        (a table by distance, made on the host)
 //   keys j with 0 <= i - j < window                (window 0: all keys)
-//   o_i = softmax_j(s_ij) v_j * sigmoid(gate_i[h]) (gate optional)
+//   o_i = softmax_j(s_ij) v_j * sigmoid(gate_i[h]) (gate optional; one per head, or one per head and value dim)
+//   with a sink: p_ij = exp(s_ij) / (exp(sink) + sum_j exp(s_ij)), one more term in the denominator that has no value
 //
 // Keys have `Dk` dims and values `Dv`; they may differ, and the two pools are shaped accordingly.
 // Scores, softmax weights and the weighted sum are float32.  One block serves the query heads of
@@ -43,7 +44,19 @@ struct BiasAttnArgs {
     int NP;                    // key partitions (grid.z); > 1: results go to part_o / part_ml and are merged after
     float* part_o;             // [N, Hq, NP, Dv]
     float* part_ml;            // [N, Hq, NP, 2]: running maximum and sum
+    int gate_per_dim;          // 0: gate column h; 1: gate column h * Dv + value dim
+    int has_sink;              // the softmax denominator holds exp(sink) beside the keys' terms
+    float sink;
 };
+
+// The sigmoid gate of output (token n, head h, value dim d); 1 without a gate.
+template <typename T>
+__device__ __forceinline__ float gate_factor(const BiasAttnArgs& a, int n, int h, int d) {
+    if (a.gate == nullptr) return 1.0f;
+    const size_t col = a.gate_per_dim ? (size_t)h * a.Dv + d : (size_t)h;
+    const float z = to_float(((const T*)a.gate)[(size_t)n * a.gate_stride + col]);
+    return 1.0f / (1.0f + expf(-z));
+}
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS) bias_attention_kernel(BiasAttnArgs a) {
@@ -74,7 +87,9 @@ __global__ void __launch_bounds__(THREADS) bias_attention_kernel(BiasAttnArgs a)
             const int g = i / Dk, d = i - g * Dk;
             qs[g][d] = to_float(q[((size_t)n * a.Hq + h0 + g) * Dk + d]);
         }
-        if (tid < HEADS) { run_max[tid] = -INFINITY; run_sum[tid] = 0.f; rescale[tid] = 0.f; }
+        // the sink is a key without a value: the first share of the keys starts from its term
+        const bool sink_here = a.has_sink && blockIdx.z == 0;
+        if (tid < HEADS) { run_max[tid] = sink_here ? a.sink : -INFINITY; run_sum[tid] = sink_here ? 1.f : 0.f; rescale[tid] = 0.f; }
         float acc[HEADS][2];
 #pragma unroll
         for (int g = 0; g < HEADS; ++g) acc[g][0] = acc[g][1] = 0.f;
@@ -164,21 +179,19 @@ __global__ void __launch_bounds__(THREADS) bias_attention_kernel(BiasAttnArgs a)
         for (int g = 0; g < HEADS; ++g) {
             if (g >= gn) continue;
             const int h = h0 + g;
-            float f = 1.0f;                              // the gate scales the output, so it may scale every part
-            if (a.gate) {
-                const float z = to_float(((const T*)a.gate)[(size_t)n * a.gate_stride + h]);
-                f = 1.0f / (1.0f + expf(-z));
-            }
+            // the gate scales the output, so it may scale every part
+            const float f0 = tid < Dv ? gate_factor<T>(a, n, h, tid) : 1.0f;
+            const float f1 = tid + THREADS < Dv ? gate_factor<T>(a, n, h, tid + THREADS) : 1.0f;
             if (a.NP == 1) {
-                f *= 1.0f / run_sum[g];
+                const float f = 1.0f / run_sum[g];
                 T* o = (T*)a.out + ((size_t)n * a.Hq + h) * Dv;
-                if (tid < Dv) o[tid] = from_float<T>(acc[g][0] * f);
-                if (tid + THREADS < Dv) o[tid + THREADS] = from_float<T>(acc[g][1] * f);
+                if (tid < Dv) o[tid] = from_float<T>(acc[g][0] * f * f0);
+                if (tid + THREADS < Dv) o[tid + THREADS] = from_float<T>(acc[g][1] * f * f1);
             } else {
                 const size_t slot = ((size_t)n * a.Hq + h) * a.NP + blockIdx.z;
                 float* o = a.part_o + slot * Dv;
-                if (tid < Dv) o[tid] = acc[g][0] * f;
-                if (tid + THREADS < Dv) o[tid + THREADS] = acc[g][1] * f;
+                if (tid < Dv) o[tid] = acc[g][0] * f0;
+                if (tid + THREADS < Dv) o[tid + THREADS] = acc[g][1] * f1;
                 if (tid == 0) {                          // an empty part has sum 0 and is skipped by the merge
                     a.part_ml[slot * 2] = run_max[g];
                     a.part_ml[slot * 2 + 1] = run_sum[g];
@@ -247,7 +260,7 @@ __global__ void __launch_bounds__(THREADS, 4) bias_attention_tile_kernel(TileArg
             const int row = i / Dk, d = i - row * Dk, qi = row / GP, g = row - qi * GP;
             Qs[i] = (qi < nq && g < gn) ? to_float(q[((size_t)(n_first + qi) * a.Hq + h0 + g) * Dk + d]) : 0.f;
         }
-        if (tid < ROWS) { run_max[tid] = -INFINITY; run_sum[tid] = 0.f; rescale[tid] = 0.f; }
+        if (tid < ROWS) { run_max[tid] = a.has_sink ? a.sink : -INFINITY; run_sum[tid] = a.has_sink ? 1.f : 0.f; rescale[tid] = 0.f; }
         float acc[ROWS];
 #pragma unroll
         for (int row = 0; row < ROWS; ++row) acc[row] = 0.f;
@@ -341,11 +354,7 @@ __global__ void __launch_bounds__(THREADS, 4) bias_attention_tile_kernel(TileArg
             const int qi = row / GP, g = row - qi * GP;
             if (qi >= nq || g >= gn || tid >= Dv) continue;
             const int h = h0 + g, n = n_first + qi;
-            float f = 1.0f / run_sum[row];
-            if (a.gate) {
-                const float z = to_float(((const T*)a.gate)[(size_t)n * a.gate_stride + h]);
-                f *= 1.0f / (1.0f + expf(-z));
-            }
+            const float f = gate_factor<T>(a, n, h, tid) / run_sum[row];
             ((T*)a.out)[((size_t)n * a.Hq + h) * Dv + tid] = from_float<T>(acc[row] * f);
         }
     }
@@ -358,7 +367,8 @@ extern "C" int sb_attention_bias(void* out, const void* q, const void* k_pool, c
                                  const int* positions, const void* gate, long long gate_stride,
                                  const float* dist_bias, int L, int N, int Hq, int Hkv, int Dk, int Dv,
                                  int page_size, int window, float scale, float cap, int num_partitions,
-                                 float* part_o, float* part_ml, int dtype, cudaStream_t stream) {
+                                 float* part_o, float* part_ml, int dtype, int gate_per_dim, int has_sink,
+                                 float sink, cudaStream_t stream) {
     SB_REQUIRE(N >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0,
                "attention_bias: %d query heads are no multiple of %d KV heads", Hq, Hkv);
     SB_REQUIRE(Dk >= 1 && Dk <= DMAX && Dv >= 1 && Dv <= 2 * THREADS,
@@ -378,6 +388,7 @@ extern "C" int sb_attention_bias(void* out, const void* q, const void* k_pool, c
     a.gate_stride = gate_stride; a.dist_bias = dist_bias; a.L = L > 0 ? L : 1; a.Hq = Hq; a.Hkv = Hkv; a.Dk = Dk;
     a.Dv = Dv; a.BS = page_size; a.window = window; a.scale = scale; a.cap = cap;
     a.NP = num_partitions; a.part_o = part_o; a.part_ml = part_ml;
+    a.gate_per_dim = gate_per_dim; a.has_sink = has_sink; a.sink = sink;
     dim3 grid(Hkv, N, num_partitions), rgrid(Hq, N);
     if (dtype == SB_F32) {
         sb::launch(bias_attention_kernel<float>, grid, dim3(THREADS), 0, stream, a);
@@ -407,7 +418,7 @@ extern "C" int sb_attention_bias_tile(void* out, const void* q, const void* k_po
                                       const int* seq_rows, const int* seq_first_pos, int R, const void* gate,
                                       long long gate_stride, const float* dist_bias, int L, int N, int Hq, int Hkv,
                                       int Dk, int Dv, int page_size, int window, float scale, float cap, int dtype,
-                                      cudaStream_t stream) {
+                                      int gate_per_dim, int has_sink, float sink, cudaStream_t stream) {
     SB_REQUIRE(sb_attention_bias_tile_supports(Hq, Hkv, Dk, Dv, dtype),
                "attention_bias_tile: heads %d/%d of %d (keys) and %d (values) are not served", Hq, Hkv, Dk, Dv);
     SB_REQUIRE((reinterpret_cast<uintptr_t>(k_pool) & 15) == 0, "attention_bias_tile: the key pool must be 16-byte aligned");
@@ -422,6 +433,7 @@ extern "C" int sb_attention_bias_tile(void* out, const void* q, const void* k_po
     a.gate_stride = gate_stride; a.dist_bias = dist_bias; a.L = L > 0 ? L : 1; a.Hq = Hq; a.Hkv = Hkv; a.Dk = Dk;
     a.Dv = Dv; a.BS = page_size; a.window = window; a.scale = scale; a.cap = cap; a.NP = 1; a.part_o = nullptr;
     a.part_ml = nullptr;
+    a.gate_per_dim = gate_per_dim; a.has_sink = has_sink; a.sink = sink;
     ta.seq_starts = seq_starts; ta.seq_rows = seq_rows; ta.seq_first_pos = seq_first_pos; ta.R = R;
     ta.GP = G >= 4 ? 4 : (G >= 2 ? 2 : 1);
     ta.QT = ROWS / ta.GP;

@@ -6,14 +6,15 @@
 using namespace sb;
 
 // ----------------------------------------------------------------------------------------
-// Embedding gather: residual[n, :] = float(table[ids[n], :]).
+// Embedding gather: residual[n, :] = float(table[ids[n], :]) * scale.
 // The residual stream is float32 in both dtypes of the engine.
 // A negative id -1 - j stands for feedback[j]: a token that an earlier kernel on the stream
 // wrote (the previous step's sample), so that a step can be launched before the host has read
 // the tokens it continues from.
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table,
-                             const int* __restrict__ ids, int d, int V, const int* __restrict__ feedback) {
+                             const int* __restrict__ ids, int d, int V, const int* __restrict__ feedback,
+                             float scale) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     const int n = blockIdx.x;
@@ -22,13 +23,14 @@ __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ tabl
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);   // ids are validated on the host; stay in bounds regardless
     const T* src = table + (size_t)id * d;
     float* dst = out + (size_t)n * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_float(src[i]);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_float(src[i]) * scale;
 }
 
 // d a multiple of 8 (bfloat16) or 4 (float32): 16-byte loads, one thread per vector.
 template <typename T>
 __global__ void embed_vec_kernel(float* __restrict__ out, const T* __restrict__ table,
-                                 const int* __restrict__ ids, int d, int V, const int* __restrict__ feedback) {
+                                 const int* __restrict__ ids, int d, int V, const int* __restrict__ feedback,
+                                 float scale) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     constexpr int VEC = Vec16<T>::N;
@@ -43,24 +45,24 @@ __global__ void embed_vec_kernel(float* __restrict__ out, const T* __restrict__ 
         v.load(src + i);
 #pragma unroll
         for (int e = 0; e < VEC; e += 4)
-            *reinterpret_cast<float4*>(dst + i + e) = make_float4(v.get(e), v.get(e + 1), v.get(e + 2), v.get(e + 3));
+            *reinterpret_cast<float4*>(dst + i + e) = make_float4(v.get(e) * scale, v.get(e + 1) * scale, v.get(e + 2) * scale, v.get(e + 3) * scale);
     }
 }
 
 // feedback: null, or int32 tokens that ids -1 - j refer to (see above).
 extern "C" int sb_embed(float* out, const void* table, const int* ids, int N, int d, int V,
-                        int dtype, const int* feedback, cudaStream_t stream) {
+                        int dtype, const int* feedback, float scale, cudaStream_t stream) {
     SB_REQUIRE(N >= 0 && d > 0 && V > 0, "embed: bad sizes N=%d d=%d V=%d", N, d, V);
     if (N == 0) return 0;
     const bool aligned = (reinterpret_cast<uintptr_t>(table) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
     if (dtype == SB_F32) {
-        if (aligned && d % 4 == 0) sb::launch(embed_vec_kernel<float>, dim3(N), dim3(256), 0, stream, out, (const float*)table, ids, d, V, feedback);
-        else sb::launch(embed_kernel<float>, dim3(N), dim3(256), 0, stream, out, (const float*)table, ids, d, V, feedback);
+        if (aligned && d % 4 == 0) sb::launch(embed_vec_kernel<float>, dim3(N), dim3(256), 0, stream, out, (const float*)table, ids, d, V, feedback, scale);
+        else sb::launch(embed_kernel<float>, dim3(N), dim3(256), 0, stream, out, (const float*)table, ids, d, V, feedback, scale);
     } else if (dtype == SB_BF16) {
         if (aligned && d % 8 == 0)
-            sb::launch(embed_vec_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, out, (const __nv_bfloat16*)table, ids, d, V, feedback);
+            sb::launch(embed_vec_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, out, (const __nv_bfloat16*)table, ids, d, V, feedback, scale);
         else
-            sb::launch(embed_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, out, (const __nv_bfloat16*)table, ids, d, V, feedback);
+            sb::launch(embed_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, out, (const __nv_bfloat16*)table, ids, d, V, feedback, scale);
     } else {
         SB_REQUIRE(false, "embed: unknown dtype %d", dtype);
     }
@@ -245,8 +247,10 @@ extern "C" int sb_add_rmsnorm(float* residual, const float* delta, int S, long l
 //   heads Hq..Hq+Hkv-1   : k  -> norm(k_gain) -> rotate -> k_pool[page, kh, off, :]
 //   heads Hq+Hkv..       : v  ->                           v_pool[page, kh, off, :]
 // page = block_table[row, pos / BS], off = pos % BS.  A null gain means no norm.
-// Rotation: angle_j = float(pos) * inv_freq[j], j < R/2; dim j pairs with j + R/2;
-// dims >= R pass through.  cosf/sinf are the accurate library functions.
+// Rotation: angle_j = float(pos) * inv_freq[j], j < R/2; dim j pairs with j + R/2, or (with
+// `neighbours`) dim 2j with dim 2j+1; dims >= R pass through.  cosf/sinf are the accurate
+// library functions.  Value heads may have another size (Dv) than query and key heads, and a
+// row of the input may be wider than the heads (`row_width`): other columns of the same product.
 // The input is either qkv in the model dtype, or (parts != null) S float32 partial sums
 // of a split-K product, added here in the order s = 0, 1, ...
 template <typename T>
@@ -256,7 +260,7 @@ __global__ void qk_norm_rope_kvwrite_kernel(
     const float* __restrict__ q_gain, const float* __restrict__ k_gain,
     const float* __restrict__ inv_freq, int R, const int* __restrict__ positions,
     const int* __restrict__ token_rows, const int* __restrict__ block_table, int table_width,
-    int BS, float eps, int Hq, int Hkv, int D, int write_kv) {
+    int BS, float eps, int Hq, int Hkv, int D, int write_kv, int Dv, int row_width, int neighbours) {
     sb::pdl_launch_dependents();     // the next kernel may begin its prologue
     sb::pdl_wait();                  // everything before this kernel is complete and visible
     __shared__ float buf[4][256];
@@ -270,10 +274,13 @@ __global__ void qk_norm_rope_kvwrite_kernel(
     const bool is_v = !is_q && !is_k;
     if (!is_q && !write_kv) return;
 
-    const size_t base = ((size_t)n * n_heads + head) * D;
+    // a row holds Hq + Hkv heads of D dims, then Hkv value heads of Dv dims (and whatever follows them)
+    const int Dh = is_v ? Dv : D;
+    const size_t base = (size_t)n * row_width + (is_v ? (size_t)(Hq + Hkv) * D + (size_t)(head - Hq - Hkv) * Dv
+                                                       : (size_t)head * D);
     float* y = buf[warp];
     float ss = 0.f;
-    for (int i = lane; i < D; i += 32) {
+    for (int i = lane; i < Dh; i += 32) {
         float v;
         if (parts != nullptr) {
             v = 0.f;
@@ -301,16 +308,19 @@ __global__ void qk_norm_rope_kvwrite_kernel(
         const int row = token_rows[n];
         const int page = block_table[(size_t)row * table_width + pos / BS];
         T* pool = is_k ? k_pool : v_pool;
-        dst = pool + (((size_t)page * Hkv + kh) * BS + (pos % BS)) * D;
+        dst = pool + (((size_t)page * Hkv + kh) * BS + (pos % BS)) * Dh;
     }
     const int half = R >> 1;
-    for (int i = lane; i < D; i += 32) {
+    for (int i = lane; i < Dh; i += 32) {
         float o = y[i];
         if (!is_v && i < R) {
-            const int j = i < half ? i : i - half;
+            // the partner of dim i and the frequency they share: halves (j, j + R/2) or neighbours (2j, 2j+1)
+            const bool first = neighbours ? (i & 1) == 0 : i < half;
+            const int j = neighbours ? i >> 1 : (first ? i : i - half);
+            const int mate = neighbours ? (i ^ 1) : (first ? i + half : i - half);
             const float ang = (float)pos * inv_freq[j];
             const float c = cosf(ang), s = sinf(ang);
-            o = i < half ? y[i] * c - y[i + half] * s : y[i] * c + y[i - half] * s;
+            o = first ? y[i] * c - y[mate] * s : y[i] * c + y[mate] * s;
         }
         dst[i] = from_float<T>(o);
     }
@@ -538,9 +548,10 @@ static void qk_launch(const void* qkv, const float* parts, int S, size_t part_st
                       void* v_pool, const float* q_gain, const float* k_gain, const float* inv_freq,
                       int rotary_dim, const int* positions, const int* token_rows, const int* block_table,
                       int table_width, int page_size, float eps, int Hq, int Hkv, int D, int N, int write_kv,
-                      cudaStream_t stream) {
-    const bool fast = (rotary_dim == D || rotary_dim == 0) && (D == 64 || D == 128 || D == 256);
+                      int Dv, int row_width, int neighbours, cudaStream_t stream) {
     const int n_heads = Hq + 2 * Hkv;
+    const bool fast = (rotary_dim == D || rotary_dim == 0) && (D == 64 || D == 128 || D == 256) && Dv == D &&
+                      row_width == n_heads * D && !(neighbours && rotary_dim > 0);
     // Heads per block: 4 (a head per warp) while that still fills the GPU, more for long batches.
     int hpb = 4;
     if (fast) {
@@ -564,7 +575,8 @@ static void qk_launch(const void* qkv, const float* parts, int S, size_t part_st
     else if (fast && D == 128) { SB_QK_FAST(4) }
     else if (fast) { SB_QK_FAST(8) }
 #undef SB_QK_FAST
-    else sb::launch(qk_norm_rope_kvwrite_kernel<T>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, D, write_kv);
+    else sb::launch(qk_norm_rope_kvwrite_kernel<T>, dim3(grid), dim3(128), 0, stream, SB_QK_ARGS, D, write_kv, Dv,
+                    row_width, neighbours);
 #undef SB_QK_ARGS
 }
 
@@ -576,7 +588,11 @@ extern "C" int sb_qk_norm_rope_kvwrite(const void* qkv, const float* parts, int 
                                        const float* inv_freq, int rotary_dim, const int* positions,
                                        const int* token_rows, const int* block_table, int table_width,
                                        int page_size, float eps, int Hq, int Hkv, int D, int N,
-                                       int write_kv, int dtype, cudaStream_t stream) {
+                                       int write_kv, int dtype, int Dv, int row_width, int neighbours,
+                                       cudaStream_t stream) {
+    SB_REQUIRE(Dv > 0 && Dv <= 256, "qk_norm_rope: value head size %d is outside 1..256", Dv);
+    SB_REQUIRE(row_width >= Hq * D + (write_kv ? Hkv * (D + Dv) : 0),
+               "qk_norm_rope: rows of %d columns do not hold the heads", row_width);
     SB_REQUIRE(N >= 0 && Hq > 0 && Hkv > 0, "qk_norm_rope: bad sizes N=%d Hq=%d Hkv=%d", N, Hq, Hkv);
     SB_REQUIRE(D > 0 && D <= 256, "qk_norm_rope: head_dim %d is outside 1..256", D);
     SB_REQUIRE(rotary_dim >= 0 && rotary_dim <= D && rotary_dim % 2 == 0,
@@ -589,11 +605,11 @@ extern "C" int sb_qk_norm_rope_kvwrite(const void* qkv, const float* parts, int 
     if (dtype == SB_F32)
         qk_launch<float>(qkv, parts, S, (size_t)part_stride, q_out, k_pool, v_pool, q_gain, k_gain, inv_freq,
                          rotary_dim, positions, token_rows, block_table, table_width, page_size, eps, Hq, Hkv, D, N,
-                         write_kv, stream);
+                         write_kv, Dv, row_width, neighbours, stream);
     else if (dtype == SB_BF16)
         qk_launch<__nv_bfloat16>(qkv, parts, S, (size_t)part_stride, q_out, k_pool, v_pool, q_gain, k_gain,
                                  inv_freq, rotary_dim, positions, token_rows, block_table, table_width, page_size,
-                                 eps, Hq, Hkv, D, N, write_kv, stream);
+                                 eps, Hq, Hkv, D, N, write_kv, Dv, row_width, neighbours, stream);
     else
         SB_REQUIRE(false, "qk_norm_rope: unknown dtype %d", dtype);
     SB_LAUNCH_CHECK();

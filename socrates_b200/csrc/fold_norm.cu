@@ -5,6 +5,8 @@
 //                   b = b / sqrt(mean(b^2) + branch_eps) * branch_gain      (if branch_gain)
 //                   v = residual[r] + b + add_rows[r] + add_vec
 //                   residual[r] = v ;  out[m] = v / sqrt(mean(v^2) + eps) * gain    (if out)
+//                   (out with a null gain: out[m] = v, the stream itself in the model dtype, for
+//                   blocks whose branches read the stream without a norm in front)
 //   normed_mean:    out[r] = scale * sum_t unit_rms(sum_s x_t[s][r]) * gain_t       (t < 2)
 //   bias_act:       out[r][f] = act(sum_s in[s][r][f] + bias[f])
 #include <math.h>
@@ -25,7 +27,7 @@ struct FoldArgs {
     float branch_eps;
     const float* add_rows;     // [rows, d] or null
     const float* add_vec;      // [d] or null
-    const float* gain;         // [d]; used with out
+    const float* gain;         // [d]; used with out; null: out is the unnormed row
     void* out;                 // [M, d] in T, or null
     const int* row_index;      // [M] or null
     int d;
@@ -77,9 +79,13 @@ __global__ void __launch_bounds__(256) fold_rmsnorm_kernel(FoldArgs a) {
         ss += v * v;
     }
     if (a.out == nullptr) return;
+    T* o = (T*)a.out + (size_t)m * d;
+    if (a.gain == nullptr) {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<T>(row[i]);
+        return;
+    }
     const float total = block_sum(ss, scratch);
     const float rinv = 1.0f / sqrtf(total / (float)d + a.eps);
-    T* o = (T*)a.out + (size_t)m * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = from_float<T>(row[i] * rinv * a.gain[i]);
 }
 
@@ -149,11 +155,12 @@ __global__ void __launch_bounds__(512) fold_rmsnorm_vec_kernel(FoldArgs a) {
         ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
     if (a.out == nullptr) return;
-    const float total = block_sum(ss, scratch);
-    const float rinv = 1.0f / sqrtf(total / (float)a.d + a.eps);
+    const bool normed = a.gain != nullptr;
+    const float rinv = normed ? 1.0f / sqrtf(block_sum(ss, scratch) / (float)a.d + a.eps) : 1.0f;
     T* o = (T*)a.out + (size_t)m * a.d;
     for (int i = threadIdx.x; i < d4; i += blockDim.x) {
-        const float4 v = row4[i], g = __ldg(reinterpret_cast<const float4*>(a.gain) + i);
+        const float4 v = row4[i];
+        const float4 g = normed ? __ldg(reinterpret_cast<const float4*>(a.gain) + i) : make_float4(1.f, 1.f, 1.f, 1.f);
         const float x0 = v.x * rinv * g.x, x1 = v.y * rinv * g.y, x2 = v.z * rinv * g.z, x3 = v.w * rinv * g.w;
         if constexpr (sizeof(T) == 2) {
             __nv_bfloat162 lo = __floats2bfloat162_rn(x0, x1), hi = __floats2bfloat162_rn(x2, x3);
@@ -247,7 +254,6 @@ extern "C" int sb_fold_rmsnorm(float* residual, const float* delta, int S, long 
                                cudaStream_t stream) {
     SB_REQUIRE(M >= 0 && d > 0 && S >= 0, "fold_rmsnorm: bad sizes M=%d d=%d S=%d", M, d, S);
     SB_REQUIRE(S == 0 || delta != nullptr, "fold_rmsnorm: S=%d partial sums but no buffer", S);
-    SB_REQUIRE(out == nullptr || gain != nullptr, "fold_rmsnorm: an output needs a gain");
     if (M == 0) return 0;
     const size_t smem = (size_t)d * sizeof(float);
     SB_REQUIRE(smem <= 200 * 1024, "fold_rmsnorm: width %d does not fit one block's shared memory", d);

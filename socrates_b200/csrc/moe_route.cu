@@ -1,0 +1,186 @@
+// Routing of a mixture-of-experts feed-forward, and the small steps around the experts' products.
+//
+//   route:       s = softmax(z) over all E router outputs (float32)
+//                c = s + correction                              (the scores experts are CHOSEN by)
+//                the E outputs form `groups` equal groups of neighbours; a group's score is its
+//                largest c; only the `keep` best groups stay (the others' c count as -inf)
+//                the `top` largest c are chosen; their weights are s (no correction, not renormalized)
+//                weights[n][e] = s_e for chosen e, else 0 ;  ids[n][k], picked[n][k] = the choices, best first
+//   scale:       act[n][e*F + f] *= weights[n][e]                (all experts' activations side by side)
+//   passthrough: slab[n][:] = x[n][:] * sum of weights[n][e] over e >= first_identity
+//                (router outputs past the real experts stand for "the input itself")
+//
+// Ties go to the lower index.  One warp routes one token.
+#include <math.h>
+
+#include "common.cuh"
+
+using namespace sb;
+
+namespace {
+
+// (value, index) of the largest value over a warp; ties go to the lower index.
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+    }
+}
+
+constexpr int ROUTE_WARPS = 4;
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
+    const float* __restrict__ logits, const float* __restrict__ correction, float* __restrict__ weights,
+    int* __restrict__ ids, float* __restrict__ picked, int N, int E, int groups, int keep, int top) {
+    sb::pdl_launch_dependents();
+    extern __shared__ float rsm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* s = rsm + (size_t)warp * (2 * E + groups);      // scores
+    float* c = s + E;                                       // choice scores
+    float* gs = c + E;                                      // group scores
+    const int n = blockIdx.x * ROUTE_WARPS + warp;
+    sb::pdl_wait();
+    if (n >= N) return;
+    const float* z = logits + (size_t)n * E;
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+        const float p = expf(z[e] - mx);
+        s[e] = p;
+        sum += p;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < E; e += 32) {
+        const float p = s[e] * inv;
+        s[e] = p;
+        c[e] = p + (correction ? correction[e] : 0.f);
+        weights[(size_t)n * E + e] = 0.f;
+    }
+    __syncwarp();
+    if (keep < groups) {
+        const int per = E / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float best = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, c[e]);
+            gs[g] = best;
+        }
+        __syncwarp();
+        // the `keep` best groups are marked with +inf, then every other group's experts are closed
+        for (int it = 0; it < keep; ++it) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32) {
+                const float v = gs[g];
+                if (v != INFINITY && (v > bv || bi == 0x7fffffff)) { bv = v; bi = g; }
+            }
+            warp_argmax(bv, bi);
+            if (lane == 0 && bi != 0x7fffffff) gs[bi] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (gs[e / per] != INFINITY) c[e] = -INFINITY;
+        __syncwarp();
+    }
+    for (int k = 0; k < top; ++k) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = c[e];
+            if (!isnan(v) && (v > bv)) { bv = v; bi = e; }
+        }
+        warp_argmax(bv, bi);
+        if (bi == 0x7fffffff) {                 // fewer open experts than `top`: nothing more to choose
+            if (lane == 0) { ids[(size_t)n * top + k] = -1; picked[(size_t)n * top + k] = 0.f; }
+            continue;
+        }
+        if (lane == 0) {
+            const float p = s[bi];
+            weights[(size_t)n * E + bi] = p;
+            ids[(size_t)n * top + k] = bi;
+            picked[(size_t)n * top + k] = p;
+            c[bi] = NAN;                         // taken
+        }
+        __syncwarp();
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_scale_kernel(T* __restrict__ act, const float* __restrict__ weights,
+                                                        int E_total, int experts, int F, size_t total) {
+    sb::pdl_launch_dependents();
+    sb::pdl_wait();
+    const size_t width = (size_t)experts * F;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = i / width;
+        const int e = (int)((i - n * width) / F);
+        const float w = weights[n * E_total + e];
+        act[i] = from_float<T>(w == 0.f ? 0.f : to_float(act[i]) * w);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_passthrough_kernel(float* __restrict__ slab, const T* __restrict__ x,
+                                                              const float* __restrict__ weights, int E_total,
+                                                              int first_identity, int d) {
+    sb::pdl_launch_dependents();
+    sb::pdl_wait();
+    const int n = blockIdx.x;
+    float w = 0.f;
+    for (int e = first_identity; e < E_total; ++e) w += weights[(size_t)n * E_total + e];
+    for (int i = threadIdx.x; i < d; i += blockDim.x) slab[(size_t)n * d + i] = w * to_float(x[(size_t)n * d + i]);
+}
+
+}  // namespace
+
+extern "C" int sb_moe_route(const float* logits, const float* correction, float* weights, int* ids, float* picked,
+                            int N, int E, int groups, int keep, int top, cudaStream_t stream) {
+    SB_REQUIRE(N >= 0 && E > 0 && top >= 1 && top <= E, "moe_route: bad sizes N=%d E=%d top=%d", N, E, top);
+    SB_REQUIRE(groups >= 1 && E % groups == 0 && keep >= 1 && keep <= groups,
+               "moe_route: %d router outputs in %d groups of which %d stay", E, groups, keep);
+    SB_REQUIRE(top <= keep * (E / groups), "moe_route: %d choices from %d open experts", top, keep * (E / groups));
+    const size_t smem = (size_t)ROUTE_WARPS * (2 * E + groups) * sizeof(float);
+    SB_REQUIRE(smem <= 48 * 1024, "moe_route: %d router outputs do not fit a block's shared memory", E);
+    if (N == 0) return 0;
+    sb::launch(moe_route_kernel, dim3((N + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, stream,
+               logits, correction, weights, ids, picked, N, E, groups, keep, top);
+    SB_LAUNCH_CHECK();
+}
+
+// act [N, experts*F] in the model dtype; weights float32 [N, E_total], the experts' first.
+extern "C" int sb_moe_scale(void* act, const float* weights, int N, int E_total, int experts, int F, int dtype,
+                            cudaStream_t stream) {
+    SB_REQUIRE(N >= 0 && experts > 0 && experts <= E_total && F > 0, "moe_scale: bad sizes N=%d experts=%d/%d F=%d", N,
+               experts, E_total, F);
+    if (N == 0) return 0;
+    const size_t total = (size_t)N * experts * F;
+    const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    if (dtype == SB_F32)
+        sb::launch(moe_scale_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)act, weights, E_total, experts, F, total);
+    else if (dtype == SB_BF16)
+        sb::launch(moe_scale_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)act, weights,
+                   E_total, experts, F, total);
+    else
+        SB_REQUIRE(false, "moe_scale: unknown dtype %d", dtype);
+    SB_LAUNCH_CHECK();
+}
+
+// slab float32 [N, d]; x [N, d] in the model dtype.
+extern "C" int sb_moe_passthrough(float* slab, const void* x, const float* weights, int N, int E_total,
+                                  int first_identity, int d, int dtype, cudaStream_t stream) {
+    SB_REQUIRE(N >= 0 && d > 0 && first_identity >= 0 && first_identity <= E_total, "moe_passthrough: bad sizes");
+    if (N == 0) return 0;
+    if (dtype == SB_F32)
+        sb::launch(moe_passthrough_kernel<float>, dim3(N), dim3(256), 0, stream, slab, (const float*)x, weights, E_total,
+                   first_identity, d);
+    else if (dtype == SB_BF16)
+        sb::launch(moe_passthrough_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, slab, (const __nv_bfloat16*)x,
+                   weights, E_total, first_identity, d);
+    else
+        SB_REQUIRE(false, "moe_passthrough: unknown dtype %d", dtype);
+    SB_LAUNCH_CHECK();
+}

@@ -27,9 +27,9 @@ P, I, F, LL = c_void_p, c_int, c_float, c_longlong
 
 _SIGNATURES = {
     "sb_abi_version": [],
-    "sb_embed": [P, P, P, I, I, I, I, P, P],
+    "sb_embed": [P, P, P, I, I, I, I, P, F, P],
     "sb_add_rmsnorm": [P, P, I, LL, P, P, P, I, I, F, I, P],
-    "sb_qk_norm_rope_kvwrite": [P, P, I, LL, P, P, P, P, P, P, I, P, P, P, I, I, F, I, I, I, I, I, I, P],
+    "sb_qk_norm_rope_kvwrite": [P, P, I, LL, P, P, P, P, P, P, I, P, P, P, I, I, F, I, I, I, I, I, I, I, I, I, P],
     "sb_silu_mul": [P, P, I, I, I, I, P],
     "sb_sample": [P, P, P, P, P, I, I, P, P],
     "sb_sample_slices": [I],
@@ -56,8 +56,13 @@ _SIGNATURES = {
     "sb_retention_chunk": [I, I],
     "sb_selective_scan": [P, LL, P, LL, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, P, LL, I, P],
     "sb_attention_bias_tile_supports": [I, I, I, I, I],
-    "sb_attention_bias_tile": [P, P, P, P, P, I, P, P, P, I, P, LL, P, I, I, I, I, I, I, I, I, F, F, I, P],
-    "sb_attention_bias": [P, P, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, I, I, F, F, I, P, P, I, P],
+    "sb_delta_rule_supports": [I, I],
+    "sb_delta_rule": [P, P, LL, I, I, I, P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
+    "sb_moe_route": [P, P, P, P, P, I, I, I, I, I, P],
+    "sb_moe_scale": [P, P, I, I, I, I, I, P],
+    "sb_moe_passthrough": [P, P, P, I, I, I, I, I, P],
+    "sb_attention_bias_tile": [P, P, P, P, P, I, P, P, P, I, P, LL, P, I, I, I, I, I, I, I, I, F, F, I, I, I, F, P],
+    "sb_attention_bias": [P, P, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, I, I, F, F, I, P, P, I, I, I, F, P],
 }
 
 

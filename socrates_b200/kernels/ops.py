@@ -68,8 +68,8 @@ def _want(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
 
 
 def embed(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor,
-          feedback: Optional[torch.Tensor] = None) -> None:
-    """out[n, :] = float32(table[ids[n], :]); out float32 [N, d], ids int32 [N].
+          feedback: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
+    """out[n, :] = float32(table[ids[n], :]) * scale; out float32 [N, d], ids int32 [N].
     With `feedback` (int32, on the device) an id -1 - j stands for feedback[j]: a token that an
     earlier kernel on the stream wrote."""
     V, d = table.shape
@@ -81,7 +81,7 @@ def embed(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor,
         _want(feedback, "feedback", torch.int32)
     lib = library()
     check(lib, lib.sb_embed(_ptr(out), _ptr(table), _ptr(ids), N, d, V, _code(table.dtype), _ptr(feedback),
-                            _stream()), "embed")
+                            float(scale), _stream()), "embed")
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: torch.Tensor,
@@ -116,15 +116,22 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optiona
                          v_pool: Optional[torch.Tensor], q_gain: Optional[torch.Tensor],
                          k_gain: Optional[torch.Tensor], inv_freq: torch.Tensor, rotary_dim: int,
                          positions: torch.Tensor, token_rows: torch.Tensor, block_table: torch.Tensor,
-                         eps: float, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+                         eps: float, num_heads: int, num_kv_heads: int, head_dim: int,
+                         value_dim: Optional[int] = None, row_width: Optional[int] = None,
+                         neighbours: bool = False) -> None:
     """Per-head norm, rotation and paged KV write for N tokens.
 
     qkv [N, (Hq+2Hkv)*D] in the model dtype, or float32 [S, N, (Hq+2Hkv)*D] partial sums
     of a split product (added here); q_out [N, Hq*D]; pools [pages, Hkv, BS, D] (None:
     the keys and values of this step are not stored, the layer reads another layer's cache).
+    `value_dim`: value heads of another size Dv (v_pool [pages, Hkv, BS, Dv]); `row_width`: the
+    rows of qkv are wider than the heads (more columns of the same product follow them; without
+    pools only the Hq query heads need be there); `neighbours`: dim 2j rotates with dim 2j+1
+    instead of dim j with dim j + rotary_dim/2.
     """
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
-    width = (Hq + 2 * Hkv) * D
+    Dv = D if value_dim is None else int(value_dim)
+    width = (Hq + Hkv) * D + Hkv * Dv if row_width is None else int(row_width)
     parts = qkv.dim() == 3
     N = qkv.shape[-2]
     if parts:
@@ -142,9 +149,9 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optiona
     page_size = 1
     if write_kv:
         _want(k_pool, "k_pool", q_out.dtype)
-        _want(v_pool, "v_pool", q_out.dtype, k_pool.shape)
         if k_pool.dim() != 4 or k_pool.shape[1] != Hkv or k_pool.shape[3] != D:
             raise KernelError(f"pools must be [pages, {Hkv}, page_size, {D}], got {tuple(k_pool.shape)}")
+        _want(v_pool, "v_pool", q_out.dtype, (*k_pool.shape[:3], Dv))
         page_size = k_pool.shape[2]
     for g, nm in ((q_gain, "q_gain"), (k_gain, "k_gain")):
         if g is not None:
@@ -154,8 +161,8 @@ def qk_norm_rope_kvwrite(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optiona
         None if parts else _ptr(qkv), _ptr(qkv) if parts else None, qkv.shape[0] if parts else 0,
         N * width, _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(q_gain), _ptr(k_gain), _ptr(inv_freq),
         rotary_dim, _ptr(positions), _ptr(token_rows), _ptr(block_table), block_table.shape[1],
-        page_size, float(eps), Hq, Hkv, D, N, int(write_kv), _code(q_out.dtype), _stream()),
-        "qk_norm_rope_kvwrite")
+        page_size, float(eps), Hq, Hkv, D, N, int(write_kv), _code(q_out.dtype), Dv, width, int(neighbours),
+        _stream()), "qk_norm_rope_kvwrite")
 
 
 def silu_mul(out: torch.Tensor, gate_up: torch.Tensor, interleaved: bool = False) -> None:
@@ -478,7 +485,8 @@ def fold_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], gain: Op
                  branch_eps: float = 0.0, add_rows: Optional[torch.Tensor] = None,
                  add_vec: Optional[torch.Tensor] = None) -> None:
     """b = sum(delta, 0) + branch_bias; with `branch_gain` b = b / sqrt(mean(b^2) + branch_eps) * branch_gain;
-    residual += b + add_rows + add_vec; out = residual / sqrt(mean(residual^2) + eps) * gain.
+    residual += b + add_rows + add_vec; out = residual / sqrt(mean(residual^2) + eps) * gain
+    (gain None with an out: out = residual, rounded to out's dtype).
 
     residual float32 [N, d]; delta float32 [S, N, d] or None; the gains, the bias and add_vec float32 [d];
     add_rows float32 [N, d]; out [M, d] in float32 or bfloat16, or None (only the residual moves on).  With
@@ -707,16 +715,27 @@ def selective_scan_scratch_size(N: int, R: int, inner: int, states: int) -> int:
     return int(library().sb_selective_scan_scratch(int(N), int(R), int(inner), int(states)))
 
 
+def _gate_stride(gate: Optional[torch.Tensor], q: torch.Tensor, N: int, columns: int) -> int:
+    if gate is None:
+        return 0
+    if gate.dtype != q.dtype or gate.dim() != 2 or gate.shape[0] != N or gate.shape[1] < columns or gate.stride(1) != 1:
+        raise KernelError(f"gate must be [{N}, >= {columns}] in {q.dtype} with unit column stride")
+    return gate.stride(0)
+
+
 def attention_bias(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                    block_table: torch.Tensor, token_rows: torch.Tensor, positions: torch.Tensor, num_heads: int,
                    scale: float, window: int = 0, softcap: float = 0.0,
                    dist_bias: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
                    num_partitions: int = 1, part_o: Optional[torch.Tensor] = None,
-                   part_ml: Optional[torch.Tensor] = None) -> None:
+                   part_ml: Optional[torch.Tensor] = None, gate_per_dim: bool = False,
+                   sink: Optional[float] = None) -> None:
     """Paged causal attention, one query per token, with scores capped by softcap * tanh(s / softcap)
     (0: no cap), a float32 bias table [Hq, L] by distance (distances past L-1 use the last entry) and a
     sigmoid gate per head (gate [N, >= Hq], head h at column h).  Keys and values may have different head
     sizes: q [N, Hq*Dk], k_pool [pages, Hkv, BS, Dk], v_pool [pages, Hkv, BS, Dv], out [N, Hq*Dv].
+    `gate_per_dim`: the gate is [N, >= Hq*Dv], one per head and value dim (column h*Dv + d).  `sink`: a score
+    whose exponential joins the softmax denominator without a value (0.0: "one added to the denominator").
     With `num_partitions` > 1 every token's visible keys are cut into that many equal shares, one block
     each, merged by a second kernel through the float32 scratch part_o (N*Hq*NP*Dv) and part_ml (N*Hq*NP*2)."""
     N = q.shape[0]
@@ -736,11 +755,7 @@ def attention_bias(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_p
         if dist_bias.dim() != 2 or dist_bias.shape[0] != Hq:
             raise KernelError(f"dist_bias must be [{Hq}, L], got {tuple(dist_bias.shape)}")
         L = dist_bias.shape[1]
-    gate_stride = 0
-    if gate is not None:
-        if gate.dtype != q.dtype or gate.dim() != 2 or gate.shape[0] != N or gate.shape[1] < Hq or gate.stride(1) != 1:
-            raise KernelError(f"gate must be [{N}, >= {Hq}] in {q.dtype} with unit column stride")
-        gate_stride = gate.stride(0)
+    gate_stride = _gate_stride(gate, q, N, Hq * Dv if gate_per_dim else Hq)
     if num_partitions > 1:
         _want(part_o, "part_o", torch.float32)
         _want(part_ml, "part_ml", torch.float32)
@@ -751,7 +766,8 @@ def attention_bias(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_p
                                      block_table.shape[1], _ptr(token_rows), _ptr(positions), _ptr(gate), gate_stride,
                                      _ptr(dist_bias), L, N, Hq, Hkv, Dk, Dv, BS, int(window), float(scale),
                                      float(softcap), int(num_partitions), _ptr(part_o), _ptr(part_ml),
-                                     _code(q.dtype), _stream()), "attention_bias",
+                                     _code(q.dtype), int(gate_per_dim), int(sink is not None),
+                                     float(sink or 0.0), _stream()), "attention_bias",
           kernels=2 if num_partitions > 1 else 1)
 
 
@@ -766,7 +782,8 @@ def attention_bias_tile(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor
                         block_table: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor,
                         seq_first_pos: torch.Tensor, num_heads: int, scale: float, window: int = 0,
                         softcap: float = 0.0, dist_bias: Optional[torch.Tensor] = None,
-                        gate: Optional[torch.Tensor] = None) -> None:
+                        gate: Optional[torch.Tensor] = None, gate_per_dim: bool = False,
+                        sink: Optional[float] = None) -> None:
     """`attention_bias` for prompt portions: request r brings tokens seq_starts[r] .. seq_starts[r+1]-1 at
     positions seq_first_pos[r], +1, ... of cache row seq_rows[r]; a block serves a tile of consecutive tokens
     of one request, so a key or value row fetched once serves all of them.  The same arithmetic in float32."""
@@ -789,14 +806,99 @@ def attention_bias_tile(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor
         if dist_bias.dim() != 2 or dist_bias.shape[0] != Hq:
             raise KernelError(f"dist_bias must be [{Hq}, L], got {tuple(dist_bias.shape)}")
         L = dist_bias.shape[1]
-    gate_stride = 0
-    if gate is not None:
-        if gate.dtype != q.dtype or gate.dim() != 2 or gate.shape[0] != N or gate.shape[1] < Hq or gate.stride(1) != 1:
-            raise KernelError(f"gate must be [{N}, >= {Hq}] in {q.dtype} with unit column stride")
-        gate_stride = gate.stride(0)
+    gate_stride = _gate_stride(gate, q, N, Hq * Dv if gate_per_dim else Hq)
     lib = library()
     check(lib, lib.sb_attention_bias_tile(_ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
                                           block_table.shape[1], _ptr(seq_starts), _ptr(seq_rows), _ptr(seq_first_pos),
                                           R, _ptr(gate), gate_stride, _ptr(dist_bias), L, N, Hq, Hkv, Dk, Dv, BS,
-                                          int(window), float(scale), float(softcap), _code(q.dtype), _stream()),
+                                          int(window), float(scale), float(softcap), _code(q.dtype),
+                                          int(gate_per_dim), int(sink is not None), float(sink or 0.0), _stream()),
           "attention_bias_tile")
+
+
+# Gated delta rule and the routing of a mixture of experts.
+
+def delta_rule_supports(key_dim: int, value_dim: int) -> bool:
+    """Whether the delta-rule kernel takes heads of these sizes (keys up to 128 dims, values up to 256)."""
+    return bool(library().sb_delta_rule_supports(int(key_dim), int(value_dim)))
+
+
+def delta_rule(out: torch.Tensor, qkv: torch.Tensor, offsets: Tuple[int, int, int], proj: torch.Tensor,
+               proj_offsets: Tuple[int, int, int], A_log: torch.Tensor, dt_bias: torch.Tensor, norm_w: torch.Tensor,
+               state: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor, num_heads: int,
+               num_key_heads: int, key_dim: int, value_dim: int, eps: float, q_scale: float) -> None:
+    """The gated delta rule over the tokens of a step, request by request, token by token.
+
+    qkv [N, >=] holds q and k (G heads of D dims, at columns offsets[0], offsets[1]) and v (H heads of Dv, at
+    offsets[2]) after their convolutions and activations; proj [N, >=] the output gate (H*Dv columns at
+    proj_offsets[0]), the write strength b and the decay input a (H columns each at proj_offsets[1], [2]).
+    Per head: q, k become unit vectors (q times q_scale), beta = sigmoid(b), g = exp(-exp(A_log) *
+    softplus(a + dt_bias)); S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; out = o / rms(o) *
+    norm_w * silu(gate).  state float32 [rows, H, D, Dv] is read and left for the next step."""
+    N = out.shape[0]
+    H, G, D, Dv = int(num_heads), int(num_key_heads), int(key_dim), int(value_dim)
+    R = seq_rows.numel()
+    _want(out, "out", None, (N, H * Dv))
+    for t, nm in ((qkv, "qkv"), (proj, "proj")):
+        if t.dim() != 2 or t.shape[0] != N or t.stride(1) != 1 or not t.is_cuda or t.dtype != out.dtype:
+            raise KernelError(f"{nm} must be a CUDA matrix of {N} rows in {out.dtype} with unit column stride")
+    if max(offsets[0], offsets[1]) + G * D > qkv.shape[1] or offsets[2] + H * Dv > qkv.shape[1]:
+        raise KernelError(f"qkv of {qkv.shape[1]} columns does not hold the heads at {offsets}")
+    if proj_offsets[0] + H * Dv > proj.shape[1] or max(proj_offsets[1], proj_offsets[2]) + H > proj.shape[1]:
+        raise KernelError(f"proj of {proj.shape[1]} columns does not hold gate, b and a at {proj_offsets}")
+    _want(A_log, "A_log", torch.float32, (H,))
+    _want(dt_bias, "dt_bias", torch.float32, (H,))
+    _want(norm_w, "norm_w", torch.float32, (Dv,))
+    _want(state, "state", torch.float32)
+    if state.shape[1:] != (H, D, Dv):
+        raise KernelError(f"state must be [rows, {H}, {D}, {Dv}], got {tuple(state.shape)}")
+    _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
+    _want(seq_rows, "seq_rows", torch.int32, (R,))
+    lib = library()
+    check(lib, lib.sb_delta_rule(_ptr(out), _ptr(qkv), qkv.stride(0), offsets[0], offsets[1], offsets[2], _ptr(proj),
+                                 proj.stride(0), proj_offsets[0], proj_offsets[1], proj_offsets[2], _ptr(A_log),
+                                 _ptr(dt_bias), _ptr(norm_w), _ptr(state), _ptr(seq_starts), _ptr(seq_rows), R, H, G,
+                                 D, Dv, float(eps), float(q_scale), _code(out.dtype), _stream()), "delta_rule")
+
+
+def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], weights: torch.Tensor, ids: torch.Tensor,
+              picked: torch.Tensor, groups: int, keep: int, top: int) -> None:
+    """Choose `top` of E router outputs per token: s = softmax(logits); chosen by s + correction among the
+    `keep` best of `groups` equal groups of neighbours (a group's score is its largest s + correction);
+    weights float32 [N, E] gets s at the chosen outputs and 0 elsewhere, ids int32 / picked float32 [N, top]
+    the choices best first."""
+    N, E = logits.shape
+    _want(logits, "logits", torch.float32)
+    if correction is not None:
+        _want(correction, "correction", torch.float32, (E,))
+    _want(weights, "weights", torch.float32, (N, E))
+    _want(ids, "ids", torch.int32, (N, top))
+    _want(picked, "picked", torch.float32, (N, top))
+    lib = library()
+    check(lib, lib.sb_moe_route(_ptr(logits), _ptr(correction), _ptr(weights), _ptr(ids), _ptr(picked), N, E,
+                                int(groups), int(keep), int(top), _stream()), "moe_route")
+
+
+def moe_scale(act: torch.Tensor, weights: torch.Tensor, experts: int) -> None:
+    """act[n, e*F + f] *= weights[n, e] for the `experts` first columns of weights; act [N, experts*F]."""
+    N, width = act.shape
+    _want(act, "act")
+    _want(weights, "weights", torch.float32)
+    if weights.shape[0] != N or weights.shape[1] < experts or width % experts:
+        raise KernelError(f"weights {tuple(weights.shape)} do not fit activations {tuple(act.shape)} of {experts} experts")
+    lib = library()
+    check(lib, lib.sb_moe_scale(_ptr(act), _ptr(weights), N, weights.shape[1], int(experts), width // experts,
+                                _code(act.dtype), _stream()), "moe_scale")
+
+
+def moe_passthrough(slab: torch.Tensor, x: torch.Tensor, weights: torch.Tensor, first_identity: int) -> None:
+    """slab[n, :] = x[n, :] * sum(weights[n, first_identity:]); slab float32 [N, d], x [N, d]."""
+    N, d = x.shape
+    _want(x, "x")
+    _want(slab, "slab", torch.float32, (N, d))
+    _want(weights, "weights", torch.float32)
+    if weights.shape[0] != N:
+        raise KernelError(f"weights {tuple(weights.shape)} for {N} tokens")
+    lib = library()
+    check(lib, lib.sb_moe_passthrough(_ptr(slab), _ptr(x), _ptr(weights), N, weights.shape[1], int(first_identity), d,
+                                      _code(x.dtype), _stream()), "moe_passthrough")

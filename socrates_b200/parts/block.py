@@ -10,7 +10,10 @@ from __future__ import annotations
 
 from typing import Dict, Mapping
 
+import torch
+
 from .base import ParamSpec, ResidualStream, build_part, register_part
+from .norm import fold_and_norm
 
 
 class PreNormBlock:
@@ -120,3 +123,47 @@ class SandwichBlock:
 
 
 register_part("arrangement", "sandwich_norm", lambda layer_spec, name="": SandwichBlock(layer_spec))
+
+
+class BranchNormBlock(SandwichBlock):
+    """A block that norms every branch on its way OUT only:
+    x = x + norm_1(mixer(x)); x = x + norm_2(feed_forward(x)).
+    Mixer and feed-forward read the stream itself.  A layer without a feed-forward has one norm.
+
+    As in the sandwich block the norm after a branch rides with the pending branch and is applied by
+    whoever folds it into the residual.  What a branch reads is the residual rounded to the model
+    dtype, written by the same folding kernel (no gain: nothing is normed); the float32 engine reads
+    the residual in place."""
+
+    def __init__(self, layer_spec):
+        want = 2 if layer_spec.feed_forward is not None else 1
+        if len(layer_spec.norms) != want:
+            raise ValueError(f"a branch_norm block with{'' if want == 2 else 'out'} a feed-forward has {want} norm(s)")
+        pre = layer_spec.prefix
+        self.norms = [build_part("norm", s, pre + s.name) for s in layer_spec.norms]
+        self.mixer = build_part("mixer", layer_spec.mixer, pre + layer_spec.mixer.name)
+        self.feed_forward = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward = build_part("feed_forward", layer_spec.feed_forward,
+                                           pre + layer_spec.feed_forward.name)
+
+    @staticmethod
+    def _stream_rows(ctx, stream: ResidualStream) -> torch.Tensor:
+        waiting = stream.pending is not None or stream.add_rows is not None or stream.add_vec is not None
+        if ctx.dtype == torch.float32:
+            if waiting:
+                fold_and_norm(stream, None, None, 0.0)
+            return stream.residual
+        out = ctx.buffers.take("stream_rows", stream.residual.shape[0], (stream.residual.shape[1],), ctx.dtype)
+        fold_and_norm(stream, None, out, 0.0)
+        return out
+
+    def forward(self, ctx, stream: ResidualStream, cache) -> None:
+        h = self._stream_rows(ctx, stream)
+        stream.pending = self._normed_on_entry(self.mixer.forward(ctx, h, cache), self.norms[0])
+        if self.feed_forward is not None:
+            h = self._stream_rows(ctx, stream)
+            stream.pending = self._normed_on_entry(self.feed_forward.forward(ctx, h), self.norms[1])
+
+
+register_part("arrangement", "branch_norm", lambda layer_spec, name="": BranchNormBlock(layer_spec))

@@ -1,7 +1,7 @@
 """Token embedding and the output head.
 
 Embedding: x = table[ids] (model/qwen/qwen_kv_paged.py:198,219), widened to the
-float32 residual.  Head: logits = x W^T with W the embedding table when the
+float32 residual and multiplied by `scale` where the plan gives one.  Head: logits = x W^T with W the embedding table when the
 configuration ties them (:224) or `lm_head.weight` otherwise; only the rows whose
 logits were asked for are computed, in float32.
 """
@@ -22,17 +22,19 @@ class Embedding(Part):
         super().__init__(spec, name)
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
+        self.tensor = self.name + str(spec.params.get("suffix", "weight"))
+        self.scale = float(spec.params.get("scale", 1.0))      # the looked-up rows times a constant, in float32
         self.table: Optional[torch.Tensor] = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
-        return {self.name + "weight": ParamSpec((self.vocab, self.hidden))}
+        return {self.tensor: ParamSpec((self.vocab, self.hidden))}
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
-        self.table = tensors[self.name + "weight"]
+        self.table = tensors[self.tensor]
 
     def forward(self, ctx) -> torch.Tensor:
         out = ctx.buffers.take("residual", ctx.num_tokens, (self.hidden,), torch.float32)
-        ops.embed(out, self.table, ctx.token_ids, ctx.token_feedback)
+        ops.embed(out, self.table, ctx.token_ids, ctx.token_feedback, self.scale)
         return out
 
 

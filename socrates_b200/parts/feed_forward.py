@@ -22,22 +22,24 @@ class SwiGLU(Part):
         super().__init__(spec, name)
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
+        # tensor names after the part's prefix: gate, up, down (a plan may rename them)
+        self.names = tuple(spec.params.get("names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
         n = self.name
         return {
-            n + "gate_proj.weight": ParamSpec((self.inter, self.hidden)),
-            n + "up_proj.weight": ParamSpec((self.inter, self.hidden)),
-            n + "down_proj.weight": ParamSpec((self.hidden, self.inter)),
+            n + self.names[0]: ParamSpec((self.inter, self.hidden)),
+            n + self.names[1]: ParamSpec((self.inter, self.hidden)),
+            n + self.names[2]: ParamSpec((self.hidden, self.inter)),
         }
 
     def bind(self, tensors: Mapping[str, torch.Tensor], dtype) -> None:
         n = self.name
-        gate, up = tensors[n + "gate_proj.weight"], tensors[n + "up_proj.weight"]
+        gate, up = tensors[n + self.names[0]], tensors[n + self.names[1]]
         self.gate_up = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.inter, self.hidden))
-        self.down = Linear(tensors[n + "down_proj.weight"])
+        self.down = Linear(tensors[n + self.names[2]])
 
     def streamed_weights(self):
         """The weight matrices in the order in which forward() reads them."""

@@ -29,7 +29,7 @@ def fold_and_norm(stream: ResidualStream, gain: Optional[torch.Tensor], out: Opt
     on the stream changes."""
     b = stream.pending
     plain = (b is None or b.plain) and stream.add_rows is None and stream.add_vec is None
-    if plain and out is not None:
+    if plain and out is not None and gain is not None:
         ops.add_rmsnorm(stream.residual, b.partial if b is not None else None, gain, out, eps, row_index)
     else:
         ops.fold_rmsnorm(stream.residual, b.partial if b is not None else None, gain, out, eps, row_index,

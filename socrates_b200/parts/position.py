@@ -2,7 +2,8 @@
 
 A position encoding hands the mixer a float32 table `inv_freq[rotary_dim/2]` and the
 number of leading dims that rotate; the kernel computes angle = float32(position) *
-inv_freq[j] and pairs dim j with j + rotary_dim/2.  Keys are stored rotated, so
+inv_freq[j] and pairs dim j with j + rotary_dim/2 (or, with `pairing: "neighbours"`, dim 2j
+with dim 2j+1: `neighbours` says which).  Keys are stored rotated, so
 positions are absolute and nothing else in the engine knows about the encoding.
 Another encoding (a fraction of the dims, scaled frequencies, none at all) is another
 table: register a class with `tables()`.
@@ -26,6 +27,10 @@ class Rotary(Part):
         self.head_dim = int(spec.params["head_dim"])
         self.rotary_dim = int(spec.params.get("rotary_dim", self.head_dim))
         self.theta = float(spec.params["theta"])
+        pairing = str(spec.params.get("pairing", "halves"))
+        if pairing not in ("halves", "neighbours"):
+            raise ValueError(f"pairing {pairing!r} is neither 'halves' nor 'neighbours'")
+        self.neighbours = pairing == "neighbours"
         if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary_dim {self.rotary_dim} must be even and at most head_dim {self.head_dim}")
         self._table: Optional[torch.Tensor] = None
@@ -58,6 +63,8 @@ class Rotary(Part):
 
 class NoPosition(Part):
     """No rotation: the mixer's kernel passes every dim through."""
+
+    neighbours = False
 
     def __init__(self, spec, name=""):
         super().__init__(spec, name)
