@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 4b|8b|32b]
     python bench.py --compare bofusun [--sizes 1k,2k,4k]     (another design beside Qwen3 at equal size)
+    python bench.py --compare loletar [--sizes 1k,2k,4k]
 
 Default run: the layer sizes of the Qwen3-4B shape (36 layers, hidden 2560, 32 query
 heads over 8 KV heads, head_dim 128, intermediate 9728, vocabulary 151936, tied head),
@@ -408,6 +409,27 @@ def _bofusun(width, layers_ret, heads, window):
             "loop": {"start": 1, "stop": layers_ret // 2 + 1, "times": 2}}
 
 
+def _loletar(width, heads):
+    """A Loletar configuration at real layer widths, eight layers: attention with heads of 128 (half of the
+    dims rotate) whose second layer reads the first one's keys and values, a gated delta rule with a
+    128 x 128 state per head, then attention again; the first layer has a dense gated feed-forward of four
+    times the width, the others eight experts of twice the width plus two identity experts, two of them a
+    token (the products a token needs equal the dense feed-forward's)."""
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+           "rot": {"dims": 64, "base": 1e6}}
+    moe = {"kind": "moe", "expert": {"ff": 2 * width},
+           "router": {"experts": 8, "identity": 2, "top": 2, "groups": {"count": 5, "keep": 3}}}
+    four = [{"type": "attention", "mixer": dict(att), "mlp": {"kind": "dense", "ff": 4 * width}},
+            {"type": "attention", "mixer": dict(att, kv_from=0), "mlp": moe},
+            {"type": "delta", "mixer": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128,
+                                        "conv": 4}, "mlp": moe},
+            {"type": "attention", "mixer": dict(att), "mlp": moe}]
+    second = [dict(l, mixer=dict(l["mixer"])) for l in four]
+    second[1]["mixer"]["kv_from"] = 4
+    return {"architecture": "Loletar", "vocab": 32000, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0}, "layers": four + second}
+
+
 def _qwen3_like(width, runs, heads):
     """The Qwen3 decoder at the same width, number of layer runs, head size and feed-forward width."""
     return {"architectures": ["Qwen3ForCausalLM"], "vocab_size": 32000, "hidden_size": width,
@@ -417,8 +439,8 @@ def _qwen3_like(width, runs, heads):
 
 
 def run_compare(args):
-    """`--compare bofusun`: prefill and decode throughput of the Bofusun design at real layer widths (random
-    weights) beside the Qwen3 decoder at equal width, layer runs and head size.  One JSON line."""
+    """`--compare bofusun|loletar`: prefill and decode throughput of another design at real layer widths
+    (random weights) beside the Qwen3 decoder at equal width, layer runs and head size.  One JSON line."""
     import torch
 
     from socrates_b200 import Engine
@@ -438,9 +460,13 @@ def run_compare(args):
     rows_out, launches = {}, 0
     for size in wanted:
         width, heads = sizes[size]
-        bof = _bofusun(width, 5, heads, 1024)
+        design = args.compare
+        bof = _bofusun(width, 5, heads, 1024) if design == "bofusun" else _loletar(width, heads)
         runs = len(config_from_dict(bof).plan().order)
-        for label, cfg_dict in (("bofusun", bof), ("qwen3", _qwen3_like(width, runs, heads))):
+        only = [x for x in (args.only.split(",") if args.only else [design, "qwen3"])]
+        for label, cfg_dict in ((design, bof), ("qwen3", _qwen3_like(width, runs, heads))):
+            if label not in only:
+                continue
             config = config_from_dict(cfg_dict)
             built = build_random_model(config, 0, torch.bfloat16, dev)
             model = built[1]
@@ -501,13 +527,13 @@ def run_compare(args):
             torch.cuda.empty_cache()
     t_end = time.perf_counter()
     sampler.stop()
-    first = rows_out[f"bofusun_{wanted[0]}"]
-    line = {"metric": f"decode tokens/s (Bofusun design, width {first['width']}, batch {B}, {ctx}-token contexts)",
+    first = next(iter(rows_out.values()))
+    line = {"metric": f"decode tokens/s ({args.compare.capitalize()} design, width {first['width']}, batch {B}, {ctx}-token contexts)",
             "value": first["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
             "ms_per_step": first["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic: random weights, token ids uniform over the vocabulary",
-            "config": {"model": "Bofusun and Qwen3 decoders at equal width and layer runs", "global_batch": B,
+            "config": {"model": f"{args.compare.capitalize()} and Qwen3 decoders at equal width and layer runs", "global_batch": B,
                        "seq_len": ctx, "prefill_tokens": T, "parallelism": "single GPU", "cuda_graph": True,
                        "l2": "inputs larger than L2 at widths 2k and 4k; a step's weights at 1k are not"},
             "clocks": sampler.summary(t_begin, t_end), "gpu_launches": launches, "impl": "ours", "compare": rows_out}
@@ -559,9 +585,10 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
-    ap.add_argument("--compare", default=None, choices=("bofusun",),
-                    help="bofusun: the Bofusun design at real layer widths beside Qwen3 at equal size "
+    ap.add_argument("--compare", default=None, choices=("bofusun", "loletar"),
+                    help="the Bofusun or the Loletar design at real layer widths beside Qwen3 at equal size "
                          "(prefill and decode); the default workload is not run")
+    ap.add_argument("--only", default=None, help="with --compare: run only these of the pair, e.g. 'loletar' or 'qwen3'")
     ap.add_argument("--sizes", default=None, help="with --compare: widths to run, of 1k,2k,4k (default 1k,2k)")
     args = ap.parse_args()
 

@@ -65,30 +65,63 @@ def attention_keys_values(h, w, pre, m, eps):
     k = (h @ w[pre + "k"].T).view(T, G, D)
     v = (h @ w[pre + "v"].T).view(T, G, Dv)
     k = rms_norm(k, w[pre + "k.norm"], eps)
-    k = rotate_pairs(k, torch.arange(T), m["rot"]["dims"], m["rot"]["base"])
+    rot = m.get("rot") or {"dims": 0, "base": 1.0}
+    k = rotate_pairs(k, torch.arange(T), rot["dims"], rot["base"])
     return k, v
 
 
-def attention_mixer(h, w, pre, m, eps, kv):
-    """kv: (keys, values) of this layer or of the layer it borrows them from."""
-    T = h.shape[0]
-    H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (h @ w[pre + "q"].T).view(T, H, D)
-    q = rms_norm(q, w[pre + "q.norm"], eps)
-    q = rotate_pairs(q, torch.arange(T), m["rot"]["dims"], m["rot"]["base"])
-    k, v = kv
-    out = torch.zeros(T, H, Dv, dtype=F64)
+def sink_attention(q, k, v, scale, sink=True):
+    """q [T, H, D], k [T, G, D], v [T, G, Dv], causal; with `sink` the denominator holds one more term of
+    score 0 that has no value.  Returns [T, H, Dv]."""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    out = torch.zeros(T, H, v.shape[2], dtype=F64)
     causal = torch.tril(torch.ones(T, T, dtype=torch.bool))
     for hd in range(H):
         g = hd // (H // G)
-        s = (q[:, hd] @ k[:, g].T) * m["scale"]
+        s = (q[:, hd] @ k[:, g].T) * scale
         s = s.masked_fill(~causal, float("-inf"))
-        mx = torch.clamp(s.max(-1, keepdim=True).values, min=0.0)
+        mx = s.max(-1, keepdim=True).values
+        if sink:
+            mx = torch.clamp(mx, min=0.0)
         e = torch.exp(s - mx)
-        p = e / (torch.exp(-mx) + e.sum(-1, keepdim=True))            # one more term of score 0 in the denominator
-        out[:, hd] = p @ v[:, g]
+        denom = e.sum(-1, keepdim=True) + (torch.exp(-mx) if sink else 0.0)
+        out[:, hd] = (e / denom) @ v[:, g]
+    return out
+
+
+def attention_mixer(h, w, pre, m, eps, kv, sink=True):
+    """kv: (keys, values) of this layer or of the layer it borrows them from."""
+    T = h.shape[0]
+    H, D, Dv = m["heads"], m["dim"], m["vdim"]
+    q = (h @ w[pre + "q"].T).view(T, H, D)
+    q = rms_norm(q, w[pre + "q.norm"], eps)
+    rot = m.get("rot") or {"dims": 0, "base": 1.0}
+    q = rotate_pairs(q, torch.arange(T), rot["dims"], rot["base"])
+    out = sink_attention(q, kv[0], kv[1], m["scale"], sink)
     gate = torch.sigmoid(h @ w[pre + "g"].T)
     return (out.reshape(T, H * Dv) * gate) @ w[pre + "o"].T
+
+
+def delta_recurrence(q, k, v, beta, decay, S0=None):
+    """q, k [T, G, D] (already unit vectors, q scaled), v [T, H, Dv], beta and decay [T, H]: per head
+    S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  Returns (o [T, H, Dv], S [H, D, Dv])."""
+    T, H, Dv = v.shape
+    G, D = q.shape[1], q.shape[2]
+    out = torch.zeros(T, H, Dv, dtype=F64)
+    S = torch.zeros(H, D, Dv, dtype=F64) if S0 is None else S0.clone()
+    for hd in range(H):
+        g = hd // (H // G)
+        for t in range(T):
+            S[hd] = decay[t, hd] * S[hd]
+            u = beta[t, hd] * (v[t, hd] - S[hd].T @ k[t, g])
+            S[hd] = S[hd] + torch.outer(k[t, g], u)
+            out[t, hd] = S[hd].T @ q[t, g]
+    return out, S
+
+
+def unit(x):
+    return x / torch.sqrt((x * x).sum(-1, keepdim=True) + 1e-6)
 
 
 def delta_mixer(h, w, pre, m, eps):
@@ -97,20 +130,10 @@ def delta_mixer(h, w, pre, m, eps):
     q = silu(causal_conv(h @ w[pre + "q"].T, w[pre + "q.conv"])).view(T, G, D)
     k = silu(causal_conv(h @ w[pre + "k"].T, w[pre + "k.conv"])).view(T, G, D)
     v = silu(causal_conv(h @ w[pre + "v"].T, w[pre + "v.conv"])).view(T, H, Dv)
-    q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
-    k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
     beta = torch.sigmoid(h @ w[pre + "b"].T)                                                   # [T, H]
     decay = torch.exp(-torch.exp(w[pre + "A_log"]) *
                       torch.nn.functional.softplus(h @ w[pre + "a"].T + w[pre + "dt_bias"]))   # [T, H]
-    out = torch.zeros(T, H, Dv, dtype=F64)
-    for hd in range(H):
-        g = hd // (H // G)
-        S = torch.zeros(D, Dv, dtype=F64)
-        for t in range(T):
-            S = decay[t, hd] * S
-            u = beta[t, hd] * (v[t, hd] - S.T @ k[t, g])
-            S = S + torch.outer(k[t, g], u)
-            out[t, hd] = S.T @ q[t, g]
+    out, _ = delta_recurrence(unit(q) * D ** -0.5, unit(k), v, beta, decay)
     out = rms_norm(out, w[pre + "norm"], eps)
     gate = silu(h @ w[pre + "g"].T).view(T, H, Dv)
     return (out * gate).reshape(T, H * Dv) @ w[pre + "o"].T
@@ -120,11 +143,11 @@ def gated_ff(h, gate, up, down):
     return (silu(h @ gate.T) * (h @ up.T)) @ down.T
 
 
-def route(h, w, pre, r):
-    """Chosen expert numbers [T, top] and their weights [T, top]."""
+def route(z, correction, r):
+    """Router outputs z [T, E] -> chosen expert numbers [T, top] and their weights [T, top]."""
     E = r["experts"] + r.get("identity", 0)
-    s = torch.softmax(h @ w[pre + "router"].T, -1)                    # [T, E]
-    choice = s + w[pre + "correction"]
+    s = torch.softmax(z, -1)                                          # [T, E]
+    choice = s + correction
     groups = r.get("groups") or {"count": 1, "keep": 1}
     n, keep = groups["count"], groups["keep"]
     per = E // n
@@ -139,11 +162,11 @@ def route(h, w, pre, r):
 
 def routed_ff(h, w, pre, mlp):
     r = mlp["router"]
-    chosen, weight = route(h, w, pre, r)
+    chosen, weight = route(h @ w[pre + "router"].T, w[pre + "correction"], r)
     out = torch.zeros(h.shape[0], w[pre + "e0.down"].shape[0], dtype=F64)
     for t in range(h.shape[0]):
         for e, p in zip(chosen[t].tolist(), weight[t]):
-            if e >= r["experts"]:
+            if e >= r["experts"]:                                     # an identity expert
                 out[t] += p * h[t]
             else:
                 x = h[t:t + 1]
@@ -151,11 +174,13 @@ def routed_ff(h, w, pre, mlp):
     return out
 
 
-def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens: List[int], streams: Optional[list] = None):
-    """Logits [T, vocab] of one sequence; `streams` collects the residual after every layer."""
+def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens: List[int], streams: Optional[list] = None,
+            sink: bool = True):
+    """Logits [T, vocab] of one sequence; `streams` collects the residual after every layer.  `sink` False
+    leaves the extra term out of the softmax (to show that a test would notice)."""
     w: Dict[str, torch.Tensor] = {k: v.to(F64) for k, v in weights.items()}
     eps = config["norm"]["eps"]
-    x = w["embed"][torch.tensor(tokens)] * config["embedding"]["scale"]
+    x = w["embed"][torch.tensor(tokens)] * (config.get("embedding") or {}).get("scale", 1.0)
     kv = {}
     for i, layer in enumerate(config["layers"]):
         pre, m = f"l{i}.mix.", layer["mixer"]
@@ -164,7 +189,7 @@ def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens: List[i
             if src is None:
                 kv[i] = attention_keys_values(x, w, pre, m, eps)
                 src = i
-            y = attention_mixer(x, w, pre, m, eps, kv[src])
+            y = attention_mixer(x, w, pre, m, eps, kv[src], sink)
         elif layer["type"] == "delta":
             y = delta_mixer(x, w, pre, m, eps)
         else:

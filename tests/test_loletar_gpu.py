@@ -1,0 +1,639 @@
+"""The Loletar decoder in the engine against the plain statement of its equations.
+
+Kernels and parts alone; the stream after every layer; whole prompts; token-by-token decoding;
+portions down to two tokens; unequal requests in one batch against each alone; rows, state slots
+and pages that are used again; a key far back that decides an attention output, in prompts and
+decoded, at page borders; the extra term of the softmax; a write far back that a recurrent state
+still holds; greedy generation through the engine's entry point and scheduler; the command line;
+a replay through bin/trace_run.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+import plain_loletar as plain
+from bofusun_tiny import Harness, rel_err
+from loletar_tiny import TINY, make_folder, save_weights
+from traces import Trace, compare, last_decoded, mixed, portions, run_trace, whole
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TOL = {torch.float32: 2e-4, torch.bfloat16: 6e-2}
+PART_TOL = {torch.float32: 1e-4, torch.bfloat16: 4e-2}
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tokens(vocab, n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def close(got, want, dtype, tol=None):
+    """float32: every row within the tolerance.  bfloat16: a token whose routing is a near-tie may choose
+    another expert than the float64 statement, which moves that row by much more than rounding; such rows
+    must stay rare (3 in 100), all others are within the tolerance."""
+    tol = TOL[dtype] if tol is None else tol
+    err = (got - want).abs().flatten(1).max(-1).values / want.abs().max()
+    if dtype == torch.float32:
+        return float(err.max()) < tol
+    return int((err >= tol).sum()) <= max(1, (3 * err.numel()) // 100) and float(err.median()) < tol
+
+
+def i32(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+# ------------------------------------------------------------------------------------------
+# kernels alone
+
+def test_scaled_embedding_and_unnormed_fold():
+    from socrates_b200.kernels import ops
+    g = torch.Generator(device=DEV).manual_seed(0)
+    table = torch.randn(11, 20, device=DEV, generator=g).bfloat16()
+    ids = i32([3, 10, 0, 3])
+    out = torch.empty(4, 20, device=DEV)
+    ops.embed(out, table, ids, None, 2.75)
+    assert torch.equal(out, table.float()[ids.long()] * 2.75)
+    # the folding kernel without a gain hands the stream on as it is, in either dtype; widths with and without 16-byte rows
+    for d in (20, 23):
+        res = torch.randn(5, d, device=DEV, generator=g)
+        delta = torch.randn(2, 5, d, device=DEV, generator=g)
+        bgain = torch.randn(d, device=DEV, generator=g)
+        v = res.double() + plain.rms_norm(delta.double().sum(0), bgain.double(), 1e-3)
+        for dt in DTYPES:
+            r, out = res.clone(), torch.empty(5, d, device=DEV, dtype=dt)
+            ops.fold_rmsnorm(r, delta, None, out, 0.0, branch_gain=bgain, branch_eps=1e-3)
+            assert torch.allclose(r.double(), v, atol=1e-5)
+            assert torch.equal(out, r.to(dt))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(3, 1, 16, 8, 6), (2, 2, 24, 24, 24), (4, 2, 8, 40, 0), (1, 1, 40, 16, 10)])
+def test_norm_rotation_in_neighbouring_pairs_and_cache_write(dtype, shape):
+    """Heads of q and k are normed and turned pair by pair (dims 2i, 2i+1), value heads of another size
+    go to their pool unchanged, and the row may hold more columns than the heads."""
+    from socrates_b200.kernels import ops
+    H, G, D, Dv, R = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    N, extra, page = 9, 5, 4
+    width = (H + G) * D + G * Dv + extra
+    x = torch.randn(N, width, generator=g).to(dtype)
+    qg, kg = torch.randn(D, generator=g), torch.randn(D, generator=g)
+    pos = [0, 1, 2, 3, 4, 5, 0, 1, 2]                      # two sequences, rows 2 and 0
+    rows = [2] * 6 + [0] * 3
+    table = i32([[5, 0], [0, 0], [1, 3]])
+    k_pool = torch.zeros(7, G, page, D, device=DEV, dtype=dtype)
+    v_pool = torch.zeros(7, G, page, Dv, device=DEV, dtype=dtype)
+    q = torch.empty(N, H * D, device=DEV, dtype=dtype)
+    freq = (50.0 ** (-torch.arange(0, max(R, 2), 2, dtype=torch.float64) / max(R, 2))).float().to(DEV)
+    ops.qk_norm_rope_kvwrite(x.to(DEV), q, k_pool, v_pool, qg.to(DEV), kg.to(DEV), freq, R, i32(pos), i32(rows),
+                             table, 1e-5, H, G, D, value_dim=Dv, row_width=width, neighbours=True)
+    xd = x.double()
+    p = torch.tensor(pos)
+    want_q = plain.rotate_pairs(plain.rms_norm(xd[:, :H * D].view(N, H, D), qg.double(), 1e-5), p, R, 50.0)
+    want_k = plain.rotate_pairs(plain.rms_norm(xd[:, H * D:(H + G) * D].view(N, G, D), kg.double(), 1e-5), p, R, 50.0)
+    want_v = xd[:, (H + G) * D:(H + G) * D + G * Dv].view(N, G, Dv)
+    tol = 1e-5 if dtype == torch.float32 else 3e-2
+    assert torch.allclose(q.double().cpu().view(N, H, D), want_q, atol=tol, rtol=tol)
+    pages = {2: [1, 3], 0: [5, 0]}
+    for n in range(N):
+        pg, off = pages[rows[n]][pos[n] // page], pos[n] % page
+        assert torch.allclose(k_pool[pg, :, off].double().cpu(), want_k[n], atol=tol, rtol=tol)
+        assert torch.equal(v_pool[pg, :, off].double().cpu(), want_v[n])
+    # a layer that reads another layer's cache brings queries only: rows of H heads (and whatever follows)
+    q2 = torch.empty_like(q)
+    xq = torch.cat([x[:, :H * D], x[:, -extra:]], 1).contiguous().to(DEV)
+    ops.qk_norm_rope_kvwrite(xq, q2, None, None, qg.to(DEV), None, freq, R, i32(pos), i32(rows), table, 1e-5, H, G, D,
+                             value_dim=Dv, row_width=H * D + extra, neighbours=True)
+    assert torch.equal(q2, q)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(6, 2, 16, 8), (2, 1, 8, 24), (5, 5, 24, 24), (3, 1, 20, 130)])
+def test_attention_with_a_sink_and_a_gate_per_dim(dtype, shape):
+    """The three forms of the kernel (one block a token, key shares that are merged, tiles of a prompt)
+    against the plain softmax with one more term in the denominator; prompts cut into portions."""
+    from socrates_b200.kernels import ops
+    H, G, D, Dv = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    T, page = 150, 16
+    q = (torch.randn(T, H, D, generator=g) * 1.5).to(dtype)
+    k = torch.randn(T, G, D, generator=g).to(dtype)
+    v = torch.randn(T, G, Dv, generator=g).to(dtype)
+    gate = torch.randn(T, H * Dv + 3, generator=g).to(dtype)
+    want = plain.sink_attention(q.double(), k.double(), v.double(), 0.4) * \
+        torch.sigmoid(gate.double()[:, :H * Dv]).view(T, H, Dv)
+    without = plain.sink_attention(q.double(), k.double(), v.double(), 0.4, sink=False) * \
+        torch.sigmoid(gate.double()[:, :H * Dv]).view(T, H, Dv)
+    assert float((want - without).abs().max()) > 0.05                      # the sink is not a detail
+    pages_needed = -(-T // page)
+    table = i32([[0] * pages_needed, list(range(pages_needed, 0, -1))])     # row 1, pages in falling order
+    k_pool = torch.zeros(pages_needed + 1, G, page, D, device=DEV, dtype=dtype)
+    v_pool = torch.zeros(pages_needed + 1, G, page, Dv, device=DEV, dtype=dtype)
+    for t in range(T):
+        pg = pages_needed - t // page
+        k_pool[pg, :, t % page] = k[t].to(DEV)
+        v_pool[pg, :, t % page] = v[t].to(DEV)
+    qf, gf = q.view(T, H * D).to(DEV), gate.to(DEV)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    pos, rows = i32(list(range(T))), i32([1] * T)
+    for NP in (1, 3, 16):
+        out = torch.empty(T, H * Dv, device=DEV, dtype=dtype)
+        po = torch.empty(T * H * NP * Dv, device=DEV) if NP > 1 else None
+        pm = torch.empty(T * H * NP * 2, device=DEV) if NP > 1 else None
+        ops.attention_bias(out, qf, k_pool, v_pool, table, rows, pos, H, 0.4, gate=gf, num_partitions=NP, part_o=po,
+                           part_ml=pm, gate_per_dim=True, sink=0.0)
+        assert torch.allclose(out.double().cpu().view(T, H, Dv), want, atol=tol, rtol=tol), NP
+    if ops.attention_bias_tile_supports(H, G, D, Dv, dtype):
+        for cuts in ([T], [70, 2, 61, 17]):
+            out, start = torch.empty(T, H * Dv, device=DEV, dtype=dtype), 0
+            for c in cuts:
+                ops.attention_bias_tile(out[start:start + c], qf[start:start + c].contiguous(), k_pool, v_pool, table,
+                                        i32([0, c]), i32([1]), i32([start]), H, 0.4, gate=gf[start:start + c],
+                                        gate_per_dim=True, sink=0.0)
+                start += c
+            assert torch.allclose(out.double().cpu().view(T, H, Dv), want, atol=tol, rtol=tol), cuts
+    else:
+        assert Dv > 128
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(4, 2, 16, 8), (1, 1, 40, 40), (2, 1, 8, 72), (3, 3, 128, 32), (2, 2, 33, 200)])
+def test_delta_rule_kernel_in_portions(dtype, shape):
+    """Three sequences of unequal length share the steps, cut at different places down to one token; the
+    states live in slots that a previous owner left dirty and `assign` cleared."""
+    from socrates_b200.kernels import ops
+    H, G, D, Dv = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    lengths, slots = [23, 6, 40], [3, 0, 1]
+    Cq, Cv = G * D, H * Dv
+    data = []
+    for n in lengths:
+        qkv = torch.randn(n, 2 * Cq + Cv + 2, generator=g).to(dtype)          # two columns that the kernel must skip
+        proj = torch.randn(n, 1 + Cv + 2 * H, generator=g).to(dtype)          # gate at column 1
+        data.append((qkv, proj))
+    A_log, dt_bias = torch.rand(H, generator=g) * 3 - 3, torch.randn(H, generator=g)
+    norm_w = 1 + 0.1 * torch.randn(Dv, generator=g)
+    want = []
+    for qkv, proj in data:
+        x, p, n = qkv.double(), proj.double(), qkv.shape[0]
+        q = plain.unit(x[:, 2:2 + Cq].view(n, G, D)) * 0.3
+        k = plain.unit(x[:, 2 + Cq:2 + 2 * Cq].view(n, G, D))
+        v = x[:, 2 + 2 * Cq:].view(n, H, Dv)
+        beta = torch.sigmoid(p[:, 1 + Cv:1 + Cv + H])
+        decay = torch.exp(-torch.exp(A_log.double()) * torch.nn.functional.softplus(p[:, 1 + Cv + H:] + dt_bias.double()))
+        o, S = plain.delta_recurrence(q, k, v, beta, decay)
+        y = plain.rms_norm(o, norm_w.double(), 1e-4) * plain.silu(p[:, 1:1 + Cv]).view(n, H, Dv)
+        want.append((y.reshape(n, Cv), S))
+    state = torch.full((4, H, D, Dv), 7.0, device=DEV)
+    state[slots] = 0.0
+    cuts = [[1, 2, 1, 5, 14], [2, 1, 1, 1, 1], [6, 1, 2, 30, 1]]
+    got, fed = [[] for _ in lengths], [0, 0, 0]
+    for step in range(5):
+        batch = [(i, cuts[i][step]) for i in range(3) if fed[i] < lengths[i]]
+        qkv = torch.cat([data[i][0][fed[i]:fed[i] + c] for i, c in batch]).to(DEV).contiguous()
+        proj = torch.cat([data[i][1][fed[i]:fed[i] + c] for i, c in batch]).to(DEV).contiguous()
+        starts = i32(np.cumsum([0] + [c for _, c in batch]).tolist())
+        out = torch.empty(qkv.shape[0], Cv, device=DEV, dtype=dtype)
+        ops.delta_rule(out, qkv, (2, 2 + Cq, 2 + 2 * Cq), proj, (1, 1 + Cv, 1 + Cv + H), A_log.to(DEV), dt_bias.to(DEV),
+                       norm_w.to(DEV), state, starts, i32([slots[i] for i, _ in batch]), H, G, D, Dv, 1e-4, 0.3)
+        at = 0
+        for i, c in batch:
+            got[i].append(out[at:at + c].double().cpu())
+            at, fed[i] = at + c, fed[i] + c
+    tol = 2e-4 if dtype == torch.float32 else 3e-2
+    for i in range(3):
+        assert fed[i] == lengths[i]
+        assert torch.allclose(torch.cat(got[i]), want[i][0], atol=tol, rtol=tol), i
+        assert torch.allclose(state[slots[i]].double().cpu(), want[i][1], atol=2e-4, rtol=2e-4), i
+    assert bool((state[2] == 7.0).all())                                   # nobody's slot stays untouched
+
+
+def test_delta_rule_refuses_heads_it_cannot_hold():
+    from socrates_b200.kernels import KernelError, ops
+    assert ops.delta_rule_supports(128, 256) and not ops.delta_rule_supports(129, 8) and not ops.delta_rule_supports(8, 257)
+    z = torch.zeros(1, 2 * 136 + 8, device=DEV)
+    with pytest.raises(KernelError):
+        ops.delta_rule(torch.zeros(1, 8, device=DEV), z, (0, 136, 272), torch.zeros(1, 10, device=DEV), (0, 8, 9),
+                       torch.zeros(1, device=DEV), torch.zeros(1, device=DEV), torch.ones(8, device=DEV),
+                       torch.zeros(1, 1, 136, 8, device=DEV), i32([0, 1]), i32([0]), 1, 1, 136, 8, 1e-5, 1.0)
+
+
+@pytest.mark.parametrize("case", [(12, 4, 4, 3, 4), (6, 0, 1, 1, 1), (5, 1, 3, 2, 2), (3, 3, 2, 1, 2), (40, 8, 6, 6, 5), (7, 0, 7, 3, 3)])
+def test_routing_kernel(case):
+    """Softmax over all outputs, the choice by score + correction inside the best groups, the weights
+    without the correction; corrections large enough to turn choices, and negative ones."""
+    from socrates_b200.kernels import ops
+    experts, identity, groups, keep, top = case
+    E, N = experts + identity, 300
+    g = torch.Generator().manual_seed(E * 7 + top)
+    z = (torch.randn(N, E, generator=g) * 2.0)
+    corr = 0.2 * torch.randn(E, generator=g) - 0.1
+    r = {"experts": experts, "identity": identity, "top": top, "groups": {"count": groups, "keep": keep}}
+    want_ids, want_w = plain.route(z.double(), corr.double(), r)
+    weights = torch.full((N, E), 9.0, device=DEV)
+    ids = torch.empty(N, top, dtype=torch.int32, device=DEV)
+    picked = torch.empty(N, top, device=DEV)
+    ops.moe_route(z.to(DEV), corr.to(DEV), weights, ids, picked, groups, keep, top)
+    # a tie or near-tie may be decided either way; it must be rare and the rest exact
+    same = (ids.cpu().long().sort(-1).values == want_ids.sort(-1).values).all(-1)
+    assert int(same.sum()) >= N - 2
+    assert torch.equal(ids.cpu().long()[same], want_ids[same])              # best first
+    assert torch.allclose(picked.cpu().double()[same], want_w[same], atol=1e-6)
+    dense = torch.zeros(N, E, dtype=torch.float64).scatter_(1, want_ids, want_w)
+    assert torch.allclose(weights.cpu().double()[same], dense[same], atol=1e-6)
+    assert int((weights != 0).sum(-1).max()) == top
+    # no correction at all is allowed too
+    ops.moe_route(z.to(DEV), None, weights, ids, picked, groups, keep, top)
+    want_ids0, _ = plain.route(z.double(), torch.zeros(E).double(), r)
+    assert int((ids.cpu().long() == want_ids0).all(-1).sum()) >= N - 2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_expert_scaling_and_passthrough_kernels(dtype):
+    from socrates_b200.kernels import ops
+    g = torch.Generator(device=DEV).manual_seed(3)
+    N, experts, identity, F, d = 6, 3, 2, 10, 12
+    act = torch.randn(N, experts * F, device=DEV, generator=g).to(dtype)
+    w = torch.rand(N, experts + identity, device=DEV, generator=g)
+    w[:, 1] = 0.0
+    w[2, 3:] = 0.0
+    want = act.double().view(N, experts, F) * w.double()[:, :experts, None]
+    scaled = act.clone()
+    ops.moe_scale(scaled, w, experts)
+    assert torch.allclose(scaled.double().view(N, experts, F), want, atol=0 if dtype == torch.float32 else 2e-2, rtol=1e-2)
+    assert bool((scaled.view(N, experts, F)[:, 1] == 0).all())
+    x = torch.randn(N, d, device=DEV, generator=g).to(dtype)
+    slab = torch.empty(N, d, device=DEV)
+    ops.moe_passthrough(slab, x, w, experts)
+    assert torch.allclose(slab.double(), x.double() * w.double()[:, experts:].sum(-1, keepdim=True), atol=1e-6)
+    assert bool((slab[2] == 0).all())
+
+
+# ------------------------------------------------------------------------------------------
+# parts alone
+
+def run_part(h, part, x, dtype, sizes, entry=None):
+    """Feed x [n, width] through a mixer (entry: its place in the run order) or a feed-forward in portions."""
+    from socrates_b200.engine.context import CacheView
+    from socrates_b200.engine.runner import StepEntry
+    n = x.shape[0]
+    h.cache.assign(1)
+    got, start, k = [], 0, 0
+    while start < n:
+        c = min(sizes[min(k, len(sizes) - 1)], n - start)
+        assert h.cache.reserve(1, start + c)
+        ctx = h.runner.prepare([StepEntry(1, [0] * c, start, [c - 1])])
+        xin = x[start:start + c].to(dtype).to(DEV).contiguous()
+        if entry is None:
+            b = part.forward(ctx, xin)
+        else:
+            b = part.forward(ctx, xin, CacheView(h.cache, entry, True))
+        got.append(b.partial.sum(0).double().cpu())
+        h.cache.commit(1, start + c)
+        start, k = start + c, k + 1
+    h.cache.release(1)
+    return torch.cat(got)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mixers_alone(tmp_path, dtype):
+    g = torch.Generator().manual_seed(4)
+    for name, layer in (("A", 0), ("A", 1), ("A", 3), ("B", 0), ("B", 1), ("B", 2), ("C", 1)):
+        folder, cfg, w = make_folder(tmp_path, name)
+        m, eps = cfg["layers"][layer]["mixer"], cfg["norm"]["eps"]
+        x = (torch.randn(70, cfg["width"], generator=g) * 1.5).bfloat16().double()
+        pre = f"l{layer}.mix."
+        if cfg["layers"][layer]["type"] == "delta":
+            want = plain.delta_mixer(x, w, pre, m, eps)
+        else:
+            want = plain.attention_mixer(x, w, pre, m, eps, plain.attention_keys_values(x, w, pre, m, eps))
+        for sizes in ((70,), (1,), (33, 2, 1, 30, 1)):
+            h = Harness(folder, dtype, max_len=96)
+            got = run_part(h, h.model.layers[layer].mixer, x, dtype, sizes, entry=layer)
+            assert float((got - want).abs().max() / want.abs().max()) < PART_TOL[dtype], (name, layer, sizes)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_feed_forwards_alone(tmp_path, dtype):
+    g = torch.Generator().manual_seed(5)
+    for name, layer in (("A", 0), ("A", 1), ("A", 3), ("B", 0), ("C", 0)):
+        folder, cfg, w = make_folder(tmp_path, name)
+        mlp = cfg["layers"][layer]["mlp"]
+        x = (torch.randn(90, cfg["width"], generator=g) * 1.2).bfloat16().double()
+        pre = f"l{layer}.mlp."
+        if mlp["kind"] == "dense":
+            want = plain.gated_ff(x, w[pre + "gate"], w[pre + "up"], w[pre + "down"])
+        else:
+            want = plain.routed_ff(x, w, pre, mlp)
+            ids, _ = plain.route(x @ w[pre + "router"].T, w[pre + "correction"], mlp["router"])
+            assert len(set(ids.flatten().tolist())) == mlp["router"]["experts"] + mlp["router"].get("identity", 0)
+        for sizes in ((90,), (1,), (64, 3, 23)):
+            h = Harness(folder, dtype, max_len=96)
+            got = run_part(h, h.model.layers[layer].feed_forward, x, dtype, sizes)
+            # a token whose choice is a near-tie may go the other way in bfloat16: judge the typical row
+            err = (got - want).abs().max(-1).values / want.abs().max()
+            assert float(err.median()) < PART_TOL[dtype] and int((err > PART_TOL[dtype]).sum()) <= (0 if dtype == torch.float32 else 3), \
+                (name, layer, sizes)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_stream_after_every_layer(tmp_path, dtype, name):
+    import socrates_b200.engine.context as C
+    from socrates_b200.parts.norm import fold_and_norm
+    folder, cfg, w = make_folder(tmp_path, name)
+    ids = tokens(cfg["vocab"], 45, 11)
+    want = []
+    plain.forward(cfg, w, ids, want)
+    h = Harness(folder, dtype)
+    got = []
+
+    def after(i, stream):
+        fold_and_norm(stream, None, None, 0.0)
+        got.append(stream.residual.double().cpu())
+
+    original = C.StepContext.__init__
+
+    def patched(self, *a, **k):
+        original(self, *a, **k)
+        self.after_run = after
+    C.StepContext.__init__ = patched
+    try:
+        h.step([("a", ids)])
+    finally:
+        C.StepContext.__init__ = original
+    assert len(got) == len(want) == len(cfg["layers"])
+    for i, (a, b) in enumerate(zip(got, want)):
+        assert close(a, b, dtype, 1e-4 if dtype == torch.float32 else 8e-2), i
+
+
+# ------------------------------------------------------------------------------------------
+# whole models
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("loletar")
+    out = {}
+    for name in TINY:
+        folder, cfg, w = make_folder(tmp, name)
+        seqs = [tokens(cfg["vocab"], n, 50 + i) for i, n in enumerate((150, 23, 77, 4))]
+        out[name] = (folder, cfg, w, seqs, [plain.forward(cfg, w, s) for s in seqs])
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_whole_prompts_decoding_and_portions(models, dtype, name):
+    folder, cfg, w, seqs, want = models[name]
+    h = Harness(folder, dtype)
+    ids, ref = seqs[0], want[0]
+    ways = {"whole": h.run("w", ids, (len(ids),)),
+            "token by token": h.run("d", ids, (1,)),
+            "pairs": h.run("p", ids, (2,)),
+            "ragged": h.run("r", ids, (7, 2, 16, 3, 2, 33, 5, 17, 2, 1, 1, 1, 40)),
+            "prompt then decoded": h.run("t", ids, (len(ids) - 100, 1))}
+    for way, got in ways.items():
+        assert close(got, ref, dtype), way
+    if dtype == torch.float32:          # how the tokens were cut changes rounding only
+        for way, got in ways.items():
+            assert rel_err(got, ways["whole"]) < 2e-5, way
+    # the first tokens of a sequence, alone
+    assert close(h.run("f", seqs[3], (1,)), want[3], dtype)
+    assert close(h.run("g", seqs[3], (4,)), want[3], dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_unequal_requests_in_one_batch(models, dtype, name):
+    """Four requests of 150, 23, 77 and 4 tokens: portions of some beside single tokens of others, a
+    request that joins late and one that sits steps out; each must come out as it does alone."""
+    folder, cfg, w, seqs, want = models[name]
+    h = Harness(folder, dtype)
+    alone = [Harness(folder, dtype).run("x", s, (len(s),)) for s in seqs] if dtype == torch.float32 else None
+    fed = [0] * 4
+    got = [[] for _ in seqs]
+    plan = [[(0, 60), (1, 1)], [(0, 1), (1, 1), (2, 30)], [(0, 2), (2, 1), (3, 4)], [(1, 20), (2, 1)],
+            [(0, 30), (1, 1), (2, 44)], [(0, 1), (2, 1)], [(0, 56)]]
+    for step in plan:
+        entries = [(f"r{i}", seqs[i][fed[i]:fed[i] + c]) for i, c in step if fed[i] < len(seqs[i])]
+        ended = [f"r{i}" for i, c in step if fed[i] < len(seqs[i]) and fed[i] + c >= len(seqs[i])]
+        out = h.step(entries, end=ended)
+        for i, c in step:
+            if f"r{i}" in out:
+                got[i].append(out[f"r{i}"])
+                fed[i] += out[f"r{i}"].shape[0]
+    for i, s in enumerate(seqs):
+        mine = torch.cat(got[i])
+        assert mine.shape[0] == len(s)
+        assert close(mine, want[i], dtype), i
+        if alone is not None:
+            assert rel_err(mine, alone[i]) < 2e-5, i
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rows_and_pages_are_used_again(models, dtype):
+    """Two rows and a pool of 12 pages of 16 slots serve eight requests one after another, in portions
+    and token by token: every state slot and page is handed out several times, dirty from its previous owner."""
+    folder, cfg, w, seqs, want = models["A"]
+    h = Harness(folder, dtype, max_rows=2, max_len=160, pages=12)
+    order = [0, 1, 2, 3, 2, 0, 3, 1]
+    for k in range(0, len(order), 2):
+        a, b = order[k], order[k + 1]
+        ga = h.run(f"a{k}", seqs[a], (31, 1, 2, 64))
+        fed, gb = 0, []
+        while fed < len(seqs[b]):                       # the second of the pair decodes token by token
+            gb.append(h.step([(f"b{k}", seqs[b][fed:fed + 1])], end=[f"b{k}"] if fed + 1 == len(seqs[b]) else [])[f"b{k}"])
+            fed += 1
+        assert close(ga, want[a], dtype) and close(torch.cat(gb), want[b], dtype), k
+    assert h.cache.free_pages() == [12, 12]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_one_far_key_decides_attention(tmp_path, dtype):
+    """The attention part of model A's layer 1 alone (its rotation switched off, so that a planted pair scores
+    high at every distance): among 430 keys the one at position `at` has by far the largest score for the last
+    queries, so that its value is most of what they read.  The key sits on the last slot of a page, on the
+    first, and in the middle; it is read in a prompt, decoded, and from an earlier portion."""
+    import copy
+    import json
+    folder, cfg, w = make_folder(tmp_path, "A")
+    cfg = copy.deepcopy(cfg)
+    cfg["layers"][1]["mixer"]["rot"] = {"dims": 0, "base": 1.0}
+    cfg["layers"][2]["mixer"]["rot"] = {"dims": 0, "base": 1.0}
+    (folder / "config.json").write_text(json.dumps(cfg))
+    m, eps, pre = cfg["layers"][1]["mixer"], cfg["norm"]["eps"], "l1.mix."
+    n, width = 430, cfg["width"]
+    g = torch.Generator().manual_seed(8)
+    for at in (15, 16, 200):
+        x = torch.randn(n, width, generator=g) * 1.5
+        u = x[at] / x[at].norm()
+        keep = x[at].clone()
+        x = x - (x @ u)[:, None] * u[None, :]           # no other input has a component along the planted key's
+        x[at] = keep
+        x = x.bfloat16().double()
+        for p in (401, 417):
+            x[p] = x[429]
+        # every dim of every head reads the planted inputs: after the per-head norm q and k are parallel
+        w2 = dict(w)
+        wk = w2[pre + "k"] + 6.0 * torch.ones(w2[pre + "k"].shape[0], 1).double() * (x[at] / x[at].norm())
+        wq = w2[pre + "q"] + 6.0 * torch.ones(w2[pre + "q"].shape[0], 1).double() * (x[429] / x[429].norm())
+        w2[pre + "k"], w2[pre + "q"] = wk.bfloat16().double(), wq.bfloat16().double()
+        w2[pre + "q.norm"] = torch.full_like(w2[pre + "q.norm"], 3.0)
+        w2[pre + "k.norm"] = torch.full_like(w2[pre + "k.norm"], 3.0)
+        save_weights(folder, w2)
+        want = plain.attention_mixer(x, w2, pre, m, eps, plain.attention_keys_values(x, w2, pre, m, eps))
+        lost = x.clone()
+        lost[at] = x[at + 1]
+        gone = plain.attention_mixer(lost, w2, pre, m, eps, plain.attention_keys_values(lost, w2, pre, m, eps))
+        assert float((gone[429] - want[429]).abs().max() / want.abs().max()) > 0.2
+        for sizes in ((n,), (400, 1), (at + 1, 2, 300, 1)):
+            h = Harness(folder, dtype, max_len=448)
+            got = run_part(h, h.model.layers[1].mixer, x, dtype, sizes, entry=1)
+            assert float((got - want).abs().max() / want.abs().max()) < PART_TOL[dtype], (at, sizes)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_write_far_back_stays_in_the_state(tmp_path, dtype):
+    """The recurrent part of model C's layer 0 with a decay close to one, queries and keys that read the first
+    half of the input only, and hundreds of nearly silent tokens in between: what tokens 0..2 wrote along a
+    key is still there when the same key comes again 400 tokens later with another value, and turns the
+    (normed) output.  Whole, decoded, and across portions."""
+    folder, cfg, w = make_folder(tmp_path, "C")
+    m, eps, pre = cfg["layers"][0]["mixer"], cfg["norm"]["eps"], "l0.mix."
+    width = cfg["width"]
+    w = dict(w)
+    w[pre + "A_log"] = torch.full_like(w[pre + "A_log"], -9.0)          # decay = exp(-e^-9 * softplus(.)): almost none
+    w[pre + "b"] = w[pre + "b"] * 0.0                                    # beta = 1/2 everywhere
+    for name in ("q", "k"):
+        t = w[pre + name].clone()
+        t[:, width // 2:] = 0.0
+        w[pre + name] = t
+    save_weights(folder, w)
+    n = 420
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(n, width, generator=g) * 1e-4                        # silent: keys far shorter than unit vectors
+    first = torch.randn(width // 2, generator=g) * 3.0
+    far, late = torch.randn(width // 2, generator=g) * 3.0, torch.randn(width // 2, generator=g) * 3.0
+    x[0:3] = torch.cat([first, far])
+    for p in (405, 419):
+        x[p - 2:p + 1] = torch.cat([first, late])                        # the same key, another value
+    x = x.bfloat16().double()
+    want = plain.delta_mixer(x, w, pre, m, eps)
+    lost = x.clone()
+    lost[:3] = x[10:13]
+    gone = plain.delta_mixer(lost, w, pre, m, eps)
+    assert float((gone[419] - want[419]).abs().max() / want.abs().max()) > 0.1
+    for sizes in ((n,), (380, 1), (3, 2, 300, 100, 1)):
+        h = Harness(folder, dtype, max_len=448)
+        got = run_part(h, h.model.layers[0].mixer, x, dtype, sizes, entry=0)
+        assert float((got - want).abs().max() / want.abs().max()) < PART_TOL[dtype], sizes
+
+
+def test_the_sink_shows_in_the_logits(models):
+    """Without the extra term in the denominator the logits move by far more than the tolerance; the
+    engine agrees with the statement that has it."""
+    folder, cfg, w, seqs, want = models["A"]
+    without = plain.forward(cfg, w, seqs[1], sink=False)
+    assert rel_err(without, want[1]) > 50 * TOL[torch.float32]
+    assert rel_err(Harness(folder, torch.float32).run("a", seqs[1], (9, 1)), want[1]) < TOL[torch.float32]
+
+
+def test_long_decoding(models):
+    """400 tokens decoded one by one after a short prompt, two requests side by side, in float32."""
+    folder, cfg, w, _, _ = models["B"]
+    a, b = tokens(cfg["vocab"], 410, 77), tokens(cfg["vocab"], 300, 78)
+    ra, rb = plain.forward(cfg, w, a), plain.forward(cfg, w, b)
+    h = Harness(folder, torch.float32, max_len=448)
+    ga, gb = [h.step([("a", a[:10])])["a"]], []
+    for t in range(10, 410):
+        entries = [("a", a[t:t + 1])]
+        if t - 10 < 300:
+            entries.append(("b", b[t - 10:t - 9]))
+        out = h.step(entries)
+        ga.append(out["a"])
+        if "b" in out:
+            gb.append(out["b"])
+    assert rel_err(torch.cat(ga), ra) < TOL[torch.float32] and rel_err(torch.cat(gb), rb) < TOL[torch.float32]
+
+
+# ------------------------------------------------------------------------------------------
+# the entry point, the scheduler, the command-line replay
+
+@pytest.mark.parametrize("dtype,graphs", [("float32", False), ("bfloat16", True)])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_through_the_entry_point(models, name, dtype, graphs):
+    """Five requests through Engine: queued, admitted as rows come free, prompts cut by the token
+    budget, decoded side by side (bfloat16: through recorded graphs), 90 new tokens each.  Every
+    produced token is the plain statement's choice, or within its margin."""
+    from socrates_b200 import Engine
+    folder, cfg, w, seqs, _ = models[name]
+    prompts = [seqs[0][:70], seqs[1], seqs[2][:40], seqs[3], seqs[0][70:101]]
+    eng = Engine(str(folder), device="cuda:0", dtype=dtype, compile=graphs, max_batch=3, max_len=192,
+                 max_new_tokens=90, token_budget=48)
+    reqs = [eng.submit(p) for p in prompts]
+    while eng.scheduler.has_work():
+        assert eng.step()
+        eng.scheduler.check()
+    margin = 1e-3 if dtype == "float32" else 8e-2
+    for p, r in zip(prompts, reqs):
+        assert r.done and len(r.output) == 90
+        logits = plain.forward(cfg, w, list(p) + r.output[:-1])
+        scale = float(logits.abs().max())
+        for i, tok in enumerate(r.output):
+            row = logits[len(p) - 1 + i]
+            best = int(torch.argmax(row))
+            assert tok == best or float(row[best] - row[tok]) <= margin * scale, (i, tok, best)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_program(models, tmp_path, dtype):
+    """bin/trace_run on model A: whole, tail decoded, portions, and a mix of up to four live requests
+    in a pool that only holds the busiest step."""
+    folder, cfg, w, seqs, want = models["A"]
+    named = {f"s{i}": s for i, s in enumerate(seqs[:3])}
+    reference = {k: want[i].numpy() for i, k in enumerate(named)}
+    trace = Trace()
+    for k, ids in named.items():
+        whole(trace, "w:" + k, ids)
+        last_decoded(trace, "d:" + k, ids, tail=20)
+        portions(trace, "p:" + k, ids)
+    mixed(trace, {f"m{j}:{k}": ids for j in range(2) for k, ids in named.items()}, seed=5, tail=20)
+    result = run_trace(folder, dtype, trace, trace.most_held, tmp_path / "out")
+    if dtype == "float32":
+        worst, where = compare(trace, result, reference, key=lambda rid: rid.split(":")[1])
+        assert worst < TOL[torch.float32], where
+    else:                                   # rows whose routing was a near-tie are judged as in `close`
+        errs = []
+        for step, rows in trace.expect.items():
+            for i, (rid, pos) in enumerate(rows):
+                ref = reference[rid.split(":")[1]]
+                errs.append(float(np.abs(result[step][i] - ref[pos]).max() / np.abs(ref).max()))
+        errs = np.array(errs)
+        assert np.isfinite(errs).all() and np.median(errs) < TOL[torch.bfloat16]
+        assert int((errs >= TOL[torch.bfloat16]).sum()) <= max(1, (3 * errs.size) // 100)
+
+
+def test_command_line(models, tmp_path):
+    """The generation command line on a Loletar folder, and on a bare config.json with random weights."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    folder, cfg, _, _, _ = models["A"]
+    common = ["--max-new-tokens", "7", "--max-len", "96", "--max-batch", "2"]
+    proc = subprocess.run([sys.executable, "-m", "socrates_b200.inference_paged", "--model", str(folder),
+                           "--num-prompts", "3", "--prompt-len", "21", "--prompt", "hello", *common],
+                          cwd=str(root), capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert "4 requests, 2 rows" in proc.stdout and "> hello" in proc.stdout
+    path = tmp_path / "config.json"
+    path.write_text(json.dumps(TINY["B"]))
+    proc = subprocess.run([sys.executable, "-m", "socrates_b200.inference_paged", "--random-config", str(path),
+                           "--num-prompts", "2", "--prompt-len", "30", "--dtype", "float32", *common],
+                          cwd=str(root), capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert "2 requests, 2 rows" in proc.stdout and "tok/s" in proc.stdout.splitlines()[-1]
