@@ -10,10 +10,14 @@
 // request's state slot; everything above is float32, only q, k, v, gate, a, b arrive in the model
 // dtype (they are matrix products and convolutions) and y leaves in it.
 //
-// A block serves one (request, value head) and walks the request's tokens of the step in order.
-// Thread j owns column j of S (Dv columns, D rows in registers): the columns of S never mix, so
-// the only exchange between threads is the sum of o^2 for the norm.  q_t and k_t sit in the lanes
-// of every warp (lane l holds dims l, l + 32, ...) and are handed round by shuffles.
+// A block serves 32 columns of the state of one (request, value head) and walks the request's tokens
+// of the step in order.  The columns of S never mix, so blocks need nothing from one another; the
+// sum of o^2 over a head's columns, the norm and the gate are a second, elementwise kernel that
+// reads the raw o.  Four neighbouring threads share a column (a quarter of the D rows each, in
+// registers; two shuffles join their partial dot products).  Tokens are staged sixteen at a time:
+// the block loads and norms their q and k once into shared memory (beta, the decay and the values
+// beside them), and while it walks them the next sixteen are already on their way into registers,
+// so the serial walk waits for no global load.
 #include <math.h>
 
 #include "common.cuh"
@@ -34,6 +38,7 @@ struct DeltaArgs {
     const float* norm_w;   // [Dv]
     float* state;          // [rows, H, D, Dv]
     void* out;             // [N, H*Dv] in T
+    float* raw_o;          // [N, H*Dv]: o before the norm and the gate
     const int* seq_starts; // [R + 1]
     const int* seq_rows;   // [R]
     int H, G, D, Dv;
@@ -42,94 +47,169 @@ struct DeltaArgs {
 
 __device__ __forceinline__ float softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
-template <typename T, int DC>
-__global__ void __launch_bounds__(256) delta_rule_kernel(DeltaArgs a) {
+constexpr int RG = 4;                 // threads that share a column of the state
+constexpr int COLS = 32;              // columns of a block
+constexpr int TB = 16;                // tokens staged at a time
+constexpr int THREADS = COLS * RG;    // 128: four warps, each stages every fourth token
+constexpr int TPW = TB / 4;           // tokens a warp stages
+
+// DR rows of the state per thread (D <= RG * DR); in shared memory the four quarters of a q or k
+// vector are DR + 4 floats apart, so that the quarters' 16-byte reads fall into different banks.
+template <typename T, int DR>
+__global__ void __launch_bounds__(THREADS) delta_rule_kernel(DeltaArgs a) {
     sb::pdl_launch_dependents();
-    __shared__ float red[2][8];
-    const int h = blockIdx.x, r = blockIdx.y;
-    const int j = threadIdx.x, lane = j & 31, warp = j >> 5, nwarps = blockDim.x >> 5;
-    const int D = a.D, Dv = a.Dv;
-    const int kh = h / (a.H / a.G);
+    constexpr int PITCH = RG * (DR + 4);
+    constexpr int DC = (RG * DR + 31) / 32;          // values of a vector per lane while staging
+    __shared__ __align__(16) float ks[TB][PITCH];
+    __shared__ __align__(16) float qs[TB][PITCH];
+    __shared__ float vs[TB][COLS], os[TB][COLS], beta_s[TB], decay_s[TB];
+    const int h = blockIdx.x, r = blockIdx.y, c0 = blockIdx.z * COLS;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int rg = tid & (RG - 1), cj = tid / RG, j = c0 + cj;
+    const int D = a.D, Dv = a.Dv, H = a.H;
+    const int kh = h / (H / a.G);
     const bool col = j < Dv;
     const float neg_rate = -expf(a.A_log[h]);
     const float dt_bias = a.dt_bias[h];
-    const float w = col ? a.norm_w[j] : 0.f;
     sb::pdl_wait();
     const int t0 = a.seq_starts[r], t1 = a.seq_starts[r + 1];
     if (t0 >= t1) return;
-    float* sp = a.state + ((size_t)a.seq_rows[r] * a.H + h) * D * Dv + j;
-    float S[DC * 32];
+    float* sp = a.state + ((size_t)a.seq_rows[r] * H + h) * D * Dv + j;
+    float S[DR];
 #pragma unroll
-    for (int i = 0; i < DC * 32; ++i) S[i] = (col && i < D) ? sp[(size_t)i * Dv] : 0.f;
-
+    for (int ii = 0; ii < DR; ++ii) {
+        const int i = rg * DR + ii;
+        S[ii] = (col && i < D) ? sp[(size_t)i * Dv] : 0.f;
+    }
     const T* qkv = (const T*)a.qkv;
     const T* proj = (const T*)a.proj;
-    for (int t = t0; t < t1; ++t) {
-        const T* xr = qkv + (size_t)t * a.qkv_stride;
-        const T* pr = proj + (size_t)t * a.proj_stride;
-        float kreg[DC], qreg[DC];
-        float kss = 0.f, qss = 0.f;
+
+    // what a thread fetches of a chunk of tokens: its warp's tokens' q and k (lane l: dims l, l + 32, ...),
+    // their b and a, and the values (token tid / 32 + 4 m, column tid % 32)
+    float kpre[TPW][DC], qpre[TPW][DC], bpre[TPW], apre[TPW], vpre[TPW];
+    auto fetch = [&](int tc) {
 #pragma unroll
-        for (int c = 0; c < DC; ++c) {
-            const int d = c * 32 + lane;
-            kreg[c] = d < D ? to_float(xr[a.k_off + kh * D + d]) : 0.f;
-            qreg[c] = d < D ? to_float(xr[a.q_off + kh * D + d]) : 0.f;
-            kss += kreg[c] * kreg[c];
-            qss += qreg[c] * qreg[c];
-        }
-        const float v = col ? to_float(xr[a.v_off + h * Dv + j]) : 0.f;
-        const float gate = col ? to_float(pr[a.gate_off + h * Dv + j]) : 0.f;
-        const float beta = 1.0f / (1.0f + expf(-to_float(pr[a.b_off + h])));
-        const float decay = expf(neg_rate * softplus(to_float(pr[a.a_off + h]) + dt_bias));
-        kss = warp_sum(kss);
-        qss = warp_sum(qss);
-        const float kinv = 1.0f / sqrtf(kss + 1e-6f), qinv = a.q_scale / sqrtf(qss + 1e-6f);
+        for (int m = 0; m < TPW; ++m) {
+            const int t = tc + warp + 4 * m;
+            const bool have = t < t1;
+            const T* xr = qkv + (size_t)(have ? t : t0) * a.qkv_stride;
+            const T* pr = proj + (size_t)(have ? t : t0) * a.proj_stride;
 #pragma unroll
-        for (int c = 0; c < DC; ++c) { kreg[c] *= kinv; qreg[c] *= qinv; }
-        // what the decayed state already answers along k
-        float rk = 0.f;
-#pragma unroll
-        for (int c = 0; c < DC; ++c)
-#pragma unroll
-            for (int l = 0; l < 32; ++l) rk = fmaf(S[c * 32 + l], __shfl_sync(0xffffffffu, kreg[c], l), rk);
-        const float u = beta * (v - decay * rk);
-        float o = 0.f;
-#pragma unroll
-        for (int c = 0; c < DC; ++c)
-#pragma unroll
-            for (int l = 0; l < 32; ++l) {
-                const float s = fmaf(__shfl_sync(0xffffffffu, kreg[c], l), u, decay * S[c * 32 + l]);
-                S[c * 32 + l] = s;
-                o = fmaf(s, __shfl_sync(0xffffffffu, qreg[c], l), o);
+            for (int c = 0; c < DC; ++c) {
+                const int d = c * 32 + lane;
+                kpre[m][c] = (have && d < D) ? to_float(xr[a.k_off + kh * D + d]) : 0.f;
+                qpre[m][c] = (have && d < D) ? to_float(xr[a.q_off + kh * D + d]) : 0.f;
             }
-        // the head's root mean square over the value dims: a sum over the block's warps
-        float ss = warp_sum(col ? o * o : 0.f);
-        if (nwarps > 1) {
-            float* rd = red[(t - t0) & 1];
-            if (lane == 0) rd[warp] = ss;
-            __syncthreads();
-            ss = 0.f;
-            for (int x = 0; x < nwarps; ++x) ss += rd[x];
+            bpre[m] = to_float(pr[a.b_off + h]);
+            apre[m] = to_float(pr[a.a_off + h]);
+            vpre[m] = (have && c0 + lane < Dv) ? to_float(xr[a.v_off + h * Dv + c0 + lane]) : 0.f;
         }
-        const float rinv = 1.0f / sqrtf(ss / (float)Dv + a.eps);
-        if (col)
-            ((T*)a.out)[(size_t)t * a.H * Dv + h * Dv + j] = from_float<T>(o * rinv * w * (gate / (1.0f + expf(-gate))));
+    };
+    fetch(t0);
+    for (int tc = t0; tc < t1; tc += TB) {
+        const int nt = min(TB, t1 - tc);
+        // ---- the fetched tokens become unit q and k, beta and the decay in shared memory
+#pragma unroll
+        for (int m = 0; m < TPW; ++m) {
+            const int tt = warp + 4 * m;
+            float kss = 0.f, qss = 0.f;
+#pragma unroll
+            for (int c = 0; c < DC; ++c) { kss += kpre[m][c] * kpre[m][c]; qss += qpre[m][c] * qpre[m][c]; }
+            kss = warp_sum(kss);
+            qss = warp_sum(qss);
+            const float kinv = 1.0f / sqrtf(kss + 1e-6f), qinv = a.q_scale / sqrtf(qss + 1e-6f);
+#pragma unroll
+            for (int c = 0; c < DC; ++c) {
+                const int d = c * 32 + lane;
+                if (d < RG * DR) {
+                    const int at = (d / DR) * (DR + 4) + d % DR;
+                    ks[tt][at] = kpre[m][c] * kinv;
+                    qs[tt][at] = qpre[m][c] * qinv;
+                }
+            }
+            vs[tt][lane] = vpre[m];
+            if (lane == 0) {
+                beta_s[tt] = 1.0f / (1.0f + expf(-bpre[m]));
+                decay_s[tt] = expf(neg_rate * softplus(apre[m] + dt_bias));
+            }
+        }
+        __syncthreads();
+        if (tc + TB < t1) fetch(tc + TB);            // in flight while this chunk is walked
+        // ---- the walk
+        for (int tt = 0; tt < nt; ++tt) {
+            const float4* k4 = reinterpret_cast<const float4*>(&ks[tt][rg * (DR + 4)]);
+            const float4* q4 = reinterpret_cast<const float4*>(&qs[tt][rg * (DR + 4)]);
+            const float decay = decay_s[tt], beta = beta_s[tt], v = vs[tt][cj];
+            float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;      // what the state already answers along k
+#pragma unroll
+            for (int x = 0; x < DR / 4; ++x) {
+                const float4 k = k4[x];
+                r0 = fmaf(S[4 * x], k.x, r0); r1 = fmaf(S[4 * x + 1], k.y, r1);
+                r2 = fmaf(S[4 * x + 2], k.z, r2); r3 = fmaf(S[4 * x + 3], k.w, r3);
+            }
+            float rk = (r0 + r1) + (r2 + r3);
+            rk += __shfl_xor_sync(0xffffffffu, rk, 1);
+            rk += __shfl_xor_sync(0xffffffffu, rk, 2);
+            const float u = beta * (v - decay * rk);
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+            for (int x = 0; x < DR / 4; ++x) {
+                const float4 k = k4[x], q = q4[x];
+                S[4 * x] = fmaf(k.x, u, decay * S[4 * x]);         o0 = fmaf(S[4 * x], q.x, o0);
+                S[4 * x + 1] = fmaf(k.y, u, decay * S[4 * x + 1]); o1 = fmaf(S[4 * x + 1], q.y, o1);
+                S[4 * x + 2] = fmaf(k.z, u, decay * S[4 * x + 2]); o2 = fmaf(S[4 * x + 2], q.z, o2);
+                S[4 * x + 3] = fmaf(k.w, u, decay * S[4 * x + 3]); o3 = fmaf(S[4 * x + 3], q.w, o3);
+            }
+            float o = (o0 + o1) + (o2 + o3);
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (rg == 0) os[tt][cj] = o;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int m = 0; m < TPW; ++m) {
+            const int tt = warp + 4 * m;
+            if (tt < nt && c0 + lane < Dv) a.raw_o[(size_t)(tc + tt) * H * Dv + h * Dv + c0 + lane] = os[tt][lane];
+        }
     }
 #pragma unroll
-    for (int i = 0; i < DC * 32; ++i)
-        if (col && i < D) sp[(size_t)i * Dv] = S[i];
+    for (int ii = 0; ii < DR; ++ii) {
+        const int i = rg * DR + ii;
+        if (col && i < D) sp[(size_t)i * Dv] = S[ii];
+    }
+}
+
+// y = o / sqrt(mean(o^2) + eps) * w * silu(gate), a warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128) delta_out_kernel(DeltaArgs a, int N) {
+    sb::pdl_launch_dependents();
+    sb::pdl_wait();
+    const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= N * a.H) return;
+    const int t = item / a.H, h = item - t * a.H, Dv = a.Dv;
+    const float* o = a.raw_o + (size_t)t * a.H * Dv + h * Dv;
+    const T* gate = (const T*)a.proj + (size_t)t * a.proj_stride + a.gate_off + h * Dv;
+    float ss = 0.f;
+    for (int j = lane; j < Dv; j += 32) ss += o[j] * o[j];
+    ss = warp_sum(ss);
+    const float rinv = 1.0f / sqrtf(ss / (float)Dv + a.eps);
+    T* y = (T*)a.out + (size_t)t * a.H * Dv + h * Dv;
+    for (int j = lane; j < Dv; j += 32) {
+        const float g = to_float(gate[j]);
+        y[j] = from_float<T>(o[j] * rinv * a.norm_w[j] * (g / (1.0f + expf(-g))));
+    }
 }
 
 template <typename T>
-int launch_delta(const DeltaArgs& a, int R, cudaStream_t stream) {
-    const int threads = ((a.Dv + 31) / 32) * 32;
-    const dim3 grid(a.H, R);
-    switch ((a.D + 31) / 32) {
-        case 1: sb::launch(delta_rule_kernel<T, 1>, grid, dim3(threads), 0, stream, a); break;
-        case 2: sb::launch(delta_rule_kernel<T, 2>, grid, dim3(threads), 0, stream, a); break;
-        case 3: sb::launch(delta_rule_kernel<T, 3>, grid, dim3(threads), 0, stream, a); break;
-        default: sb::launch(delta_rule_kernel<T, 4>, grid, dim3(threads), 0, stream, a); break;
+int launch_delta(const DeltaArgs& a, int R, int N, cudaStream_t stream) {
+    const dim3 grid(a.H, R, (a.Dv + COLS - 1) / COLS);
+    switch ((a.D + 4 * 8 - 1) / (4 * 8)) {           // rows per thread in steps of eight
+        case 1: sb::launch(delta_rule_kernel<T, 8>, grid, dim3(THREADS), 0, stream, a); break;
+        case 2: sb::launch(delta_rule_kernel<T, 16>, grid, dim3(THREADS), 0, stream, a); break;
+        case 3: sb::launch(delta_rule_kernel<T, 24>, grid, dim3(THREADS), 0, stream, a); break;
+        default: sb::launch(delta_rule_kernel<T, 32>, grid, dim3(THREADS), 0, stream, a); break;
     }
+    sb::launch(delta_out_kernel<T>, dim3((N * a.H + 3) / 4), dim3(128), 0, stream, a, N);
     SB_LAUNCH_CHECK();
 }
 
@@ -142,18 +222,19 @@ extern "C" int sb_delta_rule(void* out, const void* qkv, long long qkv_stride, i
                              const void* proj, long long proj_stride, int gate_off, int b_off, int a_off,
                              const float* A_log, const float* dt_bias, const float* norm_w, float* state,
                              const int* seq_starts, const int* seq_rows, int R, int H, int G, int D, int Dv,
-                             float eps, float q_scale, int dtype, cudaStream_t stream) {
+                             float eps, float q_scale, int dtype, float* raw_o, int N, cudaStream_t stream) {
     SB_REQUIRE(R >= 0 && H > 0 && G > 0 && H % G == 0, "delta_rule: %d value heads are no multiple of %d key heads", H, G);
     SB_REQUIRE(sb_delta_rule_supports(D, Dv), "delta_rule: heads of %d (keys, at most 128) and %d (values, at most 256) dims", D, Dv);
     SB_REQUIRE(R <= 65535, "delta_rule: %d requests exceed one launch", R);
-    if (R == 0) return 0;
+    SB_REQUIRE(raw_o != nullptr && N >= 0, "delta_rule: scratch for %d tokens is missing", N);
+    if (R == 0 || N == 0) return 0;
     DeltaArgs a;
     a.qkv = qkv; a.qkv_stride = qkv_stride; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off;
     a.proj = proj; a.proj_stride = proj_stride; a.gate_off = gate_off; a.b_off = b_off; a.a_off = a_off;
     a.A_log = A_log; a.dt_bias = dt_bias; a.norm_w = norm_w; a.state = state; a.out = out;
     a.seq_starts = seq_starts; a.seq_rows = seq_rows; a.H = H; a.G = G; a.D = D; a.Dv = Dv;
-    a.eps = eps; a.q_scale = q_scale;
-    if (dtype == SB_F32) return launch_delta<float>(a, R, stream);
-    if (dtype == SB_BF16) return launch_delta<__nv_bfloat16>(a, R, stream);
+    a.eps = eps; a.q_scale = q_scale; a.raw_o = raw_o;
+    if (dtype == SB_F32) return launch_delta<float>(a, R, N, stream);
+    if (dtype == SB_BF16) return launch_delta<__nv_bfloat16>(a, R, N, stream);
     SB_REQUIRE(false, "delta_rule: unknown dtype %d", dtype);
 }

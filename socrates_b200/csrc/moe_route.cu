@@ -1,5 +1,6 @@
 // Routing of a mixture-of-experts feed-forward, and the small steps around the experts' products.
 //
+//   logits:      z[n][e] = sum_k x[n][k] * router[e][k]        (float32 weights and sums, a block per token)
 //   route:       s = softmax(z) over all E router outputs (float32)
 //                c = s + correction                              (the scores experts are CHOSEN by)
 //                the E outputs form `groups` equal groups of neighbours; a group's score is its
@@ -109,6 +110,31 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
     }
 }
 
+// One block per token: the row of x goes to shared memory once (as float32), then every warp takes
+// every fourth router output and sums over K in a fixed order, whatever the batch holds.
+template <typename T>
+__global__ void __launch_bounds__(128) moe_logits_kernel(float* __restrict__ logits, const T* __restrict__ x,
+                                                         const float* __restrict__ router, int E, int K) {
+    sb::pdl_launch_dependents();
+    extern __shared__ float xs[];
+    const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    sb::pdl_wait();
+    for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float(x[(size_t)n * K + k]);
+    __syncthreads();
+    for (int e = warp; e < E; e += 4) {
+        const float* w = router + (size_t)e * K;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        int k = lane;
+        for (; k + 96 < K; k += 128) {
+            a0 = fmaf(xs[k], w[k], a0); a1 = fmaf(xs[k + 32], w[k + 32], a1);
+            a2 = fmaf(xs[k + 64], w[k + 64], a2); a3 = fmaf(xs[k + 96], w[k + 96], a3);
+        }
+        for (; k < K; k += 32) a0 = fmaf(xs[k], w[k], a0);
+        const float total = warp_sum((a0 + a1) + (a2 + a3));
+        if (lane == 0) logits[(size_t)n * E + e] = total;
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) moe_scale_kernel(T* __restrict__ act, const float* __restrict__ weights,
                                                         int E_total, int experts, int F, size_t total) {
@@ -120,6 +146,34 @@ __global__ void __launch_bounds__(256) moe_scale_kernel(T* __restrict__ act, con
         const int e = (int)((i - n * width) / F);
         const float w = weights[n * E_total + e];
         act[i] = from_float<T>(w == 0.f ? 0.f : to_float(act[i]) * w);
+    }
+}
+
+// F a multiple of the 16-byte vector: a thread scales one vector, whose elements share their expert.
+// An expert that was not chosen is not even read: its activations are overwritten with zeros.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_scale_vec_kernel(T* __restrict__ act, const float* __restrict__ weights,
+                                                            int E_total, int experts, int F, size_t total_vec) {
+    sb::pdl_launch_dependents();
+    sb::pdl_wait();
+    constexpr int VEC = Vec16<T>::N;
+    const size_t width_vec = (size_t)experts * F / VEC;
+    const int f_vec = F / VEC;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vec; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = i / width_vec;
+        const int e = (int)((i - n * width_vec) / f_vec);
+        const float w = weights[n * E_total + e];
+        T* p = act + i * VEC;
+        if (w == 0.f) {
+            *reinterpret_cast<uint4*>(p) = make_uint4(0u, 0u, 0u, 0u);
+            continue;
+        }
+        Vec16<T> v;
+        v.load(p);
+        alignas(16) T r[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) r[j] = from_float<T>(v.get(j) * w);
+        *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(r);
     }
 }
 
@@ -151,6 +205,33 @@ extern "C" int sb_moe_route(const float* logits, const float* correction, float*
     SB_LAUNCH_CHECK();
 }
 
+// logits float32 [N, E] = x [N, K] (model dtype) times router [E, K] (float32), transposed.
+extern "C" int sb_moe_logits(float* logits, const void* x, const float* router, int N, int E, int K, int dtype,
+                             cudaStream_t stream) {
+    SB_REQUIRE(N >= 0 && E > 0 && K > 0, "moe_logits: bad sizes N=%d E=%d K=%d", N, E, K);
+    const size_t smem = (size_t)K * sizeof(float);
+    SB_REQUIRE(smem <= 160 * 1024, "moe_logits: rows of %d values do not fit a block's shared memory", K);
+    if (N == 0) return 0;
+    static sb::OncePerDevice once_f, once_b;
+    if (dtype == SB_F32) {
+        if (smem > 48 * 1024 && !once_f.flag()) {
+            cudaFuncSetAttribute(moe_logits_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            once_f.flag() = true;
+        }
+        sb::launch(moe_logits_kernel<float>, dim3(N), dim3(128), smem, stream, logits, (const float*)x, router, E, K);
+    } else if (dtype == SB_BF16) {
+        if (smem > 48 * 1024 && !once_b.flag()) {
+            cudaFuncSetAttribute(moe_logits_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            once_b.flag() = true;
+        }
+        sb::launch(moe_logits_kernel<__nv_bfloat16>, dim3(N), dim3(128), smem, stream, logits, (const __nv_bfloat16*)x,
+                   router, E, K);
+    } else {
+        SB_REQUIRE(false, "moe_logits: unknown dtype %d", dtype);
+    }
+    SB_LAUNCH_CHECK();
+}
+
 // act [N, experts*F] in the model dtype; weights float32 [N, E_total], the experts' first.
 extern "C" int sb_moe_scale(void* act, const float* weights, int N, int E_total, int experts, int F, int dtype,
                             cudaStream_t stream) {
@@ -158,6 +239,18 @@ extern "C" int sb_moe_scale(void* act, const float* weights, int N, int E_total,
                experts, E_total, F);
     if (N == 0) return 0;
     const size_t total = (size_t)N * experts * F;
+    const int vec = dtype == SB_BF16 ? 8 : 4;
+    if (F % vec == 0 && (reinterpret_cast<uintptr_t>(act) & 15) == 0 && (dtype == SB_F32 || dtype == SB_BF16)) {
+        const size_t tv = total / vec;
+        const int vblocks = (int)((tv + 255) / 256 < 148 * 16 ? (tv + 255) / 256 : 148 * 16);
+        if (dtype == SB_F32)
+            sb::launch(moe_scale_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, (float*)act, weights, E_total,
+                       experts, F, tv);
+        else
+            sb::launch(moe_scale_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(256), 0, stream, (__nv_bfloat16*)act,
+                       weights, E_total, experts, F, tv);
+        SB_LAUNCH_CHECK();
+    }
     const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
     if (dtype == SB_F32)
         sb::launch(moe_scale_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)act, weights, E_total, experts, F, total);

@@ -57,7 +57,8 @@ _SIGNATURES = {
     "sb_selective_scan": [P, LL, P, LL, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, P, LL, I, P],
     "sb_attention_bias_tile_supports": [I, I, I, I, I],
     "sb_delta_rule_supports": [I, I],
-    "sb_delta_rule": [P, P, LL, I, I, I, P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
+    "sb_delta_rule": [P, P, LL, I, I, I, P, LL, I, I, I, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P, I, P],
+    "sb_moe_logits": [P, P, P, I, I, I, I, P],
     "sb_moe_route": [P, P, P, P, P, I, I, I, I, I, P],
     "sb_moe_scale": [P, P, I, I, I, I, I, P],
     "sb_moe_passthrough": [P, P, P, I, I, I, I, I, P],

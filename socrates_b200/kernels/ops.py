@@ -826,7 +826,8 @@ def delta_rule_supports(key_dim: int, value_dim: int) -> bool:
 def delta_rule(out: torch.Tensor, qkv: torch.Tensor, offsets: Tuple[int, int, int], proj: torch.Tensor,
                proj_offsets: Tuple[int, int, int], A_log: torch.Tensor, dt_bias: torch.Tensor, norm_w: torch.Tensor,
                state: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor, num_heads: int,
-               num_key_heads: int, key_dim: int, value_dim: int, eps: float, q_scale: float) -> None:
+               num_key_heads: int, key_dim: int, value_dim: int, eps: float, q_scale: float,
+               scratch: Optional[torch.Tensor] = None) -> None:
     """The gated delta rule over the tokens of a step, request by request, token by token.
 
     qkv [N, >=] holds q and k (G heads of D dims, at columns offsets[0], offsets[1]) and v (H heads of Dv, at
@@ -834,7 +835,9 @@ def delta_rule(out: torch.Tensor, qkv: torch.Tensor, offsets: Tuple[int, int, in
     proj_offsets[0]), the write strength b and the decay input a (H columns each at proj_offsets[1], [2]).
     Per head: q, k become unit vectors (q times q_scale), beta = sigmoid(b), g = exp(-exp(A_log) *
     softplus(a + dt_bias)); S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; out = o / rms(o) *
-    norm_w * silu(gate).  state float32 [rows, H, D, Dv] is read and left for the next step."""
+    norm_w * silu(gate).  state float32 [rows, H, D, Dv] is read and left for the next step.  `scratch`:
+    float32, at least N*H*Dv elements (o before the norm; allocated here when it is not given, which a step
+    that may be recorded into a graph must not rely on)."""
     N = out.shape[0]
     H, G, D, Dv = int(num_heads), int(num_key_heads), int(key_dim), int(value_dim)
     R = seq_rows.numel()
@@ -854,11 +857,29 @@ def delta_rule(out: torch.Tensor, qkv: torch.Tensor, offsets: Tuple[int, int, in
         raise KernelError(f"state must be [rows, {H}, {D}, {Dv}], got {tuple(state.shape)}")
     _want(seq_starts, "seq_starts", torch.int32, (R + 1,))
     _want(seq_rows, "seq_rows", torch.int32, (R,))
+    if scratch is None:
+        scratch = torch.empty(max(1, N * H * Dv), dtype=torch.float32, device=out.device)
+    _want(scratch, "scratch", torch.float32)
+    if scratch.numel() < N * H * Dv:
+        raise KernelError(f"scratch of {scratch.numel()} elements for {N * H * Dv}")
     lib = library()
     check(lib, lib.sb_delta_rule(_ptr(out), _ptr(qkv), qkv.stride(0), offsets[0], offsets[1], offsets[2], _ptr(proj),
                                  proj.stride(0), proj_offsets[0], proj_offsets[1], proj_offsets[2], _ptr(A_log),
                                  _ptr(dt_bias), _ptr(norm_w), _ptr(state), _ptr(seq_starts), _ptr(seq_rows), R, H, G,
-                                 D, Dv, float(eps), float(q_scale), _code(out.dtype), _stream()), "delta_rule")
+                                 D, Dv, float(eps), float(q_scale), _code(out.dtype), _ptr(scratch), N, _stream()),
+          "delta_rule", kernels=2)
+
+
+def moe_logits(logits: torch.Tensor, x: torch.Tensor, router: torch.Tensor) -> None:
+    """logits float32 [N, E] = x [N, K] @ router [E, K]^T with float32 weights and sums; every token's sums are
+    made in the same order whatever else the step holds."""
+    N, K = x.shape
+    E = router.shape[0]
+    _want(x, "x")
+    _want(router, "router", torch.float32, (E, K))
+    _want(logits, "logits", torch.float32, (N, E))
+    lib = library()
+    check(lib, lib.sb_moe_logits(_ptr(logits), _ptr(x), _ptr(router), N, E, K, _code(x.dtype), _stream()), "moe_logits")
 
 
 def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], weights: torch.Tensor, ids: torch.Tensor,

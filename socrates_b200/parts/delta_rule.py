@@ -12,7 +12,8 @@ The state S [H, key_dim, value_dim] is float32 and lives in the request's state 
 the last `conv_taps - 1` inputs of the convolutions, so prompts may arrive in portions and requests
 decode side by side.  Unit norms, beta, the decay, the recurrence and the output norm are float32 in
 both engines.  All six projections are one matrix product; the convolution with its activation is
-the engine's short-convolution kernel; the recurrence with everything after it is one kernel.
+the engine's short-convolution kernel; the recurrence is one kernel and the head norm with the
+gate a small second one.
 Tensors: `<name>q`, `q.conv`, `k`, `k.conv`, `v`, `v.conv`, `b`, `a`, `A_log`, `dt_bias`, `norm`, `g`, `o`.
 """
 
@@ -92,9 +93,10 @@ class GatedDeltaRule(Part):
         if tail is not None:
             ops.short_conv_tail(tail, proj, None, self.taps, ctx.seq_starts, ctx.seq_rows)
         y = ctx.buffers.take("dr_y", N, (self.Cv,), ctx.dtype)
+        raw = ctx.buffers.take("dr_raw", N, (self.Cv,), torch.float32)
         ops.delta_rule(y, conv, (0, self.Cqk, 2 * self.Cqk), proj, (C, C + self.Cv, C + self.Cv + self.H),
                        self.A_log, self.dt_bias, self.norm_w, cache.state("S"), ctx.seq_starts, ctx.seq_rows,
-                       self.H, self.G, self.dk, self.dv, self.eps, self.q_scale)
+                       self.H, self.G, self.dk, self.dv, self.eps, self.q_scale, scratch=raw)
         return Branch(self.o(ctx, y, self.out_buffer, out="partial"))
 
 

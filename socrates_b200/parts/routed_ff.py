@@ -83,7 +83,7 @@ class RoutedFeedForward(Part):
         N = x.shape[0]
         take = ctx.buffers.take
         logits = take("moe_logits", N, (self.E,), torch.float32)
-        ops.gemm_simt(logits, x, self.router)
+        ops.moe_logits(logits, x, self.router)
         weights = take("moe_weights", N, (self.E,), torch.float32)
         ids = take("moe_ids", N, (self.top,), torch.int32)
         picked = take("moe_picked", N, (self.top,), torch.float32)
