@@ -191,7 +191,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
                             const int* __restrict__ block_table, int table_width,
                             const int* __restrict__ seq_starts, const int* __restrict__ seq_rows,
                             const int* __restrict__ seq_first_pos, int R, int Hq, int Hkv, int BS, int window,
-                            float scale_log2, int* __restrict__ status) {
+                            float scale_log2, int* __restrict__ status, const bf16* __restrict__ gate,
+                            long long gate_stride, int gate_per_dim, int has_sink, float sink_raw) {
     constexpr int PANELS = D / 64;                         // 64-dim panels of 128-byte rows
     constexpr int PANEL_Q = ROWS * 128;                    // bytes of one Q panel
     constexpr int PANEL_KV = KTILE * 128;                  // bytes of one K or V panel
@@ -388,7 +389,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
         }
     } else if (active) {
         // =============================================================== the softmax warps
-        float m_ref = -INFINITY, l_run = 0.f;
+        // with a sink the denominator starts from one more term: a score (sink_raw, before the scale) that has
+        // no value.  It is the first reference maximum, and its weight 2^0 = 1 the first sum.
+        float m_ref = has_sink ? sink_raw : -INFINITY, l_run = has_sink ? 1.f : 0.f;
         const int tok = tid / G, g = tid - tok * G;
         const int qpos = tok < n_tok ? first_pos + tok : -1;   // rows past the tile see no key
         const int qlo = (window > 0 && qpos + 1 > window) ? qpos + 1 - window : 0;
@@ -529,12 +532,26 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
                 tc_fence_after();
                 const float inv = 1.0f / l_run;
                 uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)(t0 + (tok < n_tok ? tok : 0)) * Hq + kh * G + g) * D);
+                // an output gate: sigmoid of one value per head, or per head and dim
+                const bf16* grow_ptr = gate ? gate + (size_t)(t0 + (tok < n_tok ? tok : 0)) * gate_stride +
+                                                  (gate_per_dim ? (size_t)(kh * G + g) * D : (size_t)(kh * G + g)) : nullptr;
+                float head_gate = 1.0f;
+                if (gate && !gate_per_dim && tok < n_tok) head_gate = 1.0f / (1.0f + __expf(-__bfloat162float(grow_ptr[0])));
 #pragma unroll
                 for (int c = 0; c < D; c += 32) {
                     uint32_t ov[32];
                     tmem_ld32(lane_base + COL_O + c, ov);
                     tmem_ld_wait();
                     if (tok < n_tok) {
+                        float* fo = reinterpret_cast<float*>(ov);
+                        if (gate && gate_per_dim) {
+#pragma unroll
+                            for (int x = 0; x < 32; ++x)
+                                fo[x] *= 1.0f / (1.0f + expf(-__bfloat162float(grow_ptr[c + x])));
+                        } else if (gate) {
+#pragma unroll
+                            for (int x = 0; x < 32; ++x) fo[x] *= head_gate;
+                        }
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const float* f = reinterpret_cast<const float*>(ov) + 8 * j;
@@ -563,7 +580,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
 template <int D>
 int launch(const CUtensorMap& mk, const CUtensorMap& mv, void* out, const void* q, const int* block_table,
            int table_width, const int* seq_starts, const int* seq_rows, const int* seq_first_pos, int R, int N,
-           int Hq, int Hkv, int BS, int window, float scale, int* status, cudaStream_t stream) {
+           int Hq, int Hkv, int BS, int window, float scale, int* status, const void* gate, long long gate_stride,
+           int gate_per_dim, int has_sink, float sink, cudaStream_t stream) {
     auto kernel = attn_prefill_tcgen05_kernel<D>;
     static sb::OncePerDevice once_per_device;
     bool& configured = once_per_device.flag();
@@ -577,7 +595,8 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, void* out, const void* 
     dim3 grid((N / TQ + R) * Hkv);                           // an upper bound of the number of tiles, times heads
     sb::launch(kernel, grid, dim3(THREADS), smem_bytes<D>() + table_width * 4, stream, mk, mv, (bf16*)out,
                (const bf16*)q, block_table, table_width, seq_starts, seq_rows, seq_first_pos, R, Hq, Hkv, BS, window,
-               scale * LOG2E, status);
+               scale * LOG2E, status, (const bf16*)gate, gate_stride, gate_per_dim, has_sink,
+               has_sink ? sink / scale : 0.f);
     return 0;
 }
 
@@ -592,13 +611,17 @@ extern "C" int sb_attention_tcgen05_supports(int Hq, int Hkv, int D, int page_si
 }
 
 // Arguments as sb_attention_prefill_mma, plus `num_pages` (pages of the pools, the null
-// page included) and the status word of the bounded waits.
+// page included) and the status word of the bounded waits.  Optional: a sigmoid output gate
+// (`gate` [N, gate_stride] bfloat16, one column per head, or per head and dim) and a sink (a score
+// whose exponential joins the denominator without a value).
 extern "C" int sb_attention_prefill_tcgen05(void* out, const void* q, const void* k_pool, const void* v_pool,
                                             int num_pages, const int* block_table, int table_width,
                                             const int* seq_starts, const int* seq_rows,
                                             const int* seq_first_pos, int R, int N, int Hq, int Hkv, int D,
                                             int page_size, int window, float scale, int* status,
-                                            cudaStream_t stream) {
+                                            const void* gate, long long gate_stride, int gate_per_dim, int has_sink,
+                                            float sink, cudaStream_t stream) {
+    SB_REQUIRE(!has_sink || scale > 0.f, "attention_tcgen05: a sink needs a positive scale");
     SB_REQUIRE(sb_attention_tcgen05_supports(Hq, Hkv, D, page_size),
                "attention_tcgen05: Hq=%d Hkv=%d head_dim=%d page_size=%d is not supported", Hq, Hkv, D, page_size);
     SB_REQUIRE(R > 0 && N > 0 && window >= 0 && table_width > 0 && table_width <= 4096 && num_pages > 0,
@@ -614,10 +637,10 @@ extern "C" int sb_attention_prefill_tcgen05(void* out, const void* q, const void
     int rc;
     if (D == 64)
         rc = launch<64>(mk, mv, out, q, block_table, table_width, seq_starts, seq_rows, seq_first_pos, R, N, Hq, Hkv,
-                        page_size, window, scale, status, stream);
+                        page_size, window, scale, status, gate, gate_stride, gate_per_dim, has_sink, sink, stream);
     else
         rc = launch<128>(mk, mv, out, q, block_table, table_width, seq_starts, seq_rows, seq_first_pos, R, N, Hq,
-                         Hkv, page_size, window, scale, status, stream);
+                         Hkv, page_size, window, scale, status, gate, gate_stride, gate_per_dim, has_sink, sink, stream);
     if (rc != 0) return rc;
     SB_LAUNCH_CHECK();
 }

@@ -46,7 +46,7 @@ _SIGNATURES = {
     "sb_attention_decode_stream_supports": [I, I, I, I],
     "sb_attention_decode_stream": [P, P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, I, P],
     "sb_attention_tcgen05_supports": [I, I, I, I],
-    "sb_attention_prefill_tcgen05": [P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P],
+    "sb_attention_prefill_tcgen05": [P, P, P, P, I, P, I, P, P, P, I, I, I, I, I, I, I, F, P, P, LL, I, I, F, P],
     "sb_fold_rmsnorm": [P, P, I, LL, P, P, F, P, P, P, P, P, I, I, F, I, P],
     "sb_normed_mean": [P, P, I, LL, P, P, I, LL, P, I, I, F, F, P],
     "sb_bias_act": [P, P, P, I, LL, P, I, I, I, I, P],

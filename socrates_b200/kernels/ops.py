@@ -450,7 +450,8 @@ def attention_tcgen05_supports(num_heads: int, num_kv_heads: int, head_dim: int,
 def attention_prefill_tcgen05(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                               block_table: torch.Tensor, seq_starts: torch.Tensor, seq_rows: torch.Tensor,
                               seq_first_pos: torch.Tensor, num_heads: int, scale: float, status: torch.Tensor,
-                              window: int = 0) -> None:
+                              window: int = 0, gate: Optional[torch.Tensor] = None, gate_per_dim: bool = False,
+                              sink: Optional[float] = None) -> None:
     """Paged causal attention of prompt portions on tcgen05 (scores and P.V in tensor
     memory, pages brought in by TMA).  Arguments as `attention_prefill_mma`, plus the int32
     status word that receives a non-zero code if a bounded wait inside the kernel gave up."""
@@ -466,11 +467,15 @@ def attention_prefill_tcgen05(out: torch.Tensor, q: torch.Tensor, k_pool: torch.
     _want(seq_rows, "seq_rows", torch.int32, (R,))
     _want(seq_first_pos, "seq_first_pos", torch.int32, (R,))
     _want(status, "status", torch.int32)
+    # optional: out *= sigmoid(gate) (gate [N, >= Hq] or, with gate_per_dim, [N, >= Hq*D], bfloat16) and a sink,
+    # a score whose exponential joins the softmax denominator without a value
+    gate_stride = _gate_stride(gate, q, N, num_heads * D if gate_per_dim else num_heads)
     lib = library()
     check(lib, lib.sb_attention_prefill_tcgen05(
         _ptr(out), _ptr(q), _ptr(k_pool), _ptr(v_pool), pages, _ptr(block_table), block_table.shape[1],
         _ptr(seq_starts), _ptr(seq_rows), _ptr(seq_first_pos), R, N, num_heads, Hkv, D, BS, int(window),
-        float(scale), _ptr(status), _stream()), "attention_prefill_tcgen05")
+        float(scale), _ptr(status), _ptr(gate), gate_stride, int(gate_per_dim), int(sink is not None),
+        float(sink or 0.0), _stream()), "attention_prefill_tcgen05")
 
 
 # ---------------------------------------------------------------------------------------------

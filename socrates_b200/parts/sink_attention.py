@@ -9,7 +9,8 @@ QK-RMSNorm, rotation, keys and values of different sizes, and an output gate.
 
 The gate is one value per head and value dim ("dim") or one per head ("head"), read from the same
 input as the projections.  Scores, weights and the weighted sum are float32 (the CUDA-core attention
-kernels); keys are stored normed and rotated, so a layer with `own_kv: False` (its run reads an
+kernels; prompt portions in the bfloat16 engine with keys and values of one size of 64 or 128 run on the
+tensor-core tile kernel, whose weights are two bfloat16 terms); keys are stored normed and rotated, so a layer with `own_kv: False` (its run reads an
 earlier run's cache) has no k, v or k-norm tensors and brings only its queries, mask and gate.
 All projections of a layer are one matrix product.
 Tensors: `<name>q`, `k`, `v`, `q.norm`, `k.norm`, `g`, `o`.
@@ -113,7 +114,15 @@ class GatedSinkAttention(Part):
         attn = ctx.buffers.take("sa_attn", N, (self.H * self.dv,), ctx.dtype)
         gate = proj[:, self.Cq + self.Ckv:] if self.gate is not None else None
         per_dim = self.gate == "dim"
-        if (not ctx.all_decode and N >= 4 * ctx.num_seqs
+        if (not ctx.all_decode and ctx.dtype == torch.bfloat16 and ctx.status is not None and self.dk == self.dv
+                and ops.attention_tcgen05_supports(self.H, self.G, self.dk, k_pool.shape[2])):
+            # prompt portions in the bfloat16 engine, keys and values of one size: the tensor-core tile kernel.
+            # Scores are float32 sums of the bfloat16 q and k that the cache holds anyway; softmax is float32;
+            # each weight enters the value product as two bfloat16 terms (16 bits of mantissa).
+            ops.attention_prefill_tcgen05(attn, q, k_pool, v_pool, table, ctx.seq_starts, ctx.seq_rows,
+                                          ctx.seq_first_pos, self.H, self.scale, ctx.status, self.window or 0,
+                                          gate=gate, gate_per_dim=per_dim, sink=self.sink)
+        elif (not ctx.all_decode and N >= 4 * ctx.num_seqs
                 and ops.attention_bias_tile_supports(self.H, self.G, self.dk, self.dv, ctx.dtype)):
             # prompt portions: a tile of a request's consecutive tokens per block shares the keys it reads
             ops.attention_bias_tile(attn, q, k_pool, v_pool, table, ctx.seq_starts, ctx.seq_rows, ctx.seq_first_pos,

@@ -55,6 +55,14 @@ TINY = {
               {"type": "delta", "mixer": _delta(1, 1, 40, 40, 1), "mlp": _dense(56)},
               {"type": "delta", "mixer": _delta(2, 1, 8, 72, 4), "mlp": None},
               {"type": "attention", "mixer": _att(3, 3, 24, 24, None, None, 0.2, kv_from=0), "mlp": _dense(24)}]},
+    # keys and values of one size, 64 and 128: in the bfloat16 engine prompt portions of these layers run on the
+    # tensor-core attention kernel; one router output per group
+    "D": {"architecture": "Loletar", "vocab": 80, "width": 64, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+          "layers": [
+              {"type": "attention", "mixer": _att(4, 2, 64, 64, 32, 10000.0, 0.125), "mlp": _dense(48)},
+              {"type": "attention", "mixer": _att(4, 2, 64, 64, 32, 10000.0, 0.125, kv_from=0), "mlp": _moe(16, 4, 1, 2, 5, 2)},
+              {"type": "attention", "mixer": _att(2, 1, 128, 128, 128, 500000.0, 0.09), "mlp": None},
+              {"type": "delta", "mixer": _delta(2, 2, 64, 64, 4), "mlp": _dense(40)}]},
     # recurrent layers only: no pages at all; as many identity experts as real ones, one group of two kept
     "C": {"architecture": "Loletar", "vocab": 300, "width": 32, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.5},
           "layers": [
