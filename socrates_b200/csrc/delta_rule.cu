@@ -14,10 +14,11 @@
 // of the step in order.  The columns of S never mix, so blocks need nothing from one another; the
 // sum of o^2 over a head's columns, the norm and the gate are a second, elementwise kernel that
 // reads the raw o.  Four neighbouring threads share a column (a quarter of the D rows each, in
-// registers; two shuffles join their partial dot products).  Tokens are staged sixteen at a time:
-// the block loads and norms their q and k once into shared memory (beta, the decay and the values
-// beside them), and while it walks them the next sixteen are already on their way into registers,
-// so the serial walk waits for no global load.
+// registers; two shuffles join their partial dot products).  Tokens are staged sixteen at a time
+// by four more warps of the block: they load q and k, make them unit vectors and leave them in
+// shared memory with beta, the decay and the values beside them, into one of two buffers while the
+// walking warps are busy with the other, so the serial walk waits neither for a global load nor for
+// a norm, an exponential or a logarithm.
 #include <math.h>
 
 #include "common.cuh"
@@ -50,8 +51,10 @@ __device__ __forceinline__ float softplus(float x) { return x > 20.f ? x : log1p
 constexpr int RG = 4;                 // threads that share a column of the state
 constexpr int COLS = 32;              // columns of a block
 constexpr int TB = 16;                // tokens staged at a time
-constexpr int THREADS = COLS * RG;    // 128: four warps, each stages every fourth token
-constexpr int TPW = TB / 4;           // tokens a warp stages
+constexpr int WALKERS = COLS * RG;    // 128 threads walk the tokens ...
+constexpr int STAGERS = 128;          // ... and 128 prepare the next ones meanwhile
+constexpr int THREADS = WALKERS + STAGERS;
+constexpr int TPW = TB / (STAGERS / 32);     // tokens a staging warp prepares
 
 // DR rows of the state per thread (D <= RG * DR); in shared memory the four quarters of a q or k
 // vector are DR + 4 floats apart, so that the quarters' 16-byte reads fall into different banks.
@@ -60,61 +63,43 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(DeltaArgs a) {
     sb::pdl_launch_dependents();
     constexpr int PITCH = RG * (DR + 4);
     constexpr int DC = (RG * DR + 31) / 32;          // values of a vector per lane while staging
-    __shared__ __align__(16) float ks[TB][PITCH];
-    __shared__ __align__(16) float qs[TB][PITCH];
-    __shared__ float vs[TB][COLS], os[TB][COLS], beta_s[TB], decay_s[TB];
+    __shared__ __align__(16) float ks[2][TB][PITCH];
+    __shared__ __align__(16) float qs[2][TB][PITCH];
+    __shared__ float vs[2][TB][COLS], beta_s[2][TB], decay_s[2][TB], os[TB][COLS];
     const int h = blockIdx.x, r = blockIdx.y, c0 = blockIdx.z * COLS;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int rg = tid & (RG - 1), cj = tid / RG, j = c0 + cj;
+    const bool walker = tid < WALKERS;
     const int D = a.D, Dv = a.Dv, H = a.H;
     const int kh = h / (H / a.G);
-    const bool col = j < Dv;
     const float neg_rate = -expf(a.A_log[h]);
     const float dt_bias = a.dt_bias[h];
     sb::pdl_wait();
     const int t0 = a.seq_starts[r], t1 = a.seq_starts[r + 1];
     if (t0 >= t1) return;
-    float* sp = a.state + ((size_t)a.seq_rows[r] * H + h) * D * Dv + j;
-    float S[DR];
-#pragma unroll
-    for (int ii = 0; ii < DR; ++ii) {
-        const int i = rg * DR + ii;
-        S[ii] = (col && i < D) ? sp[(size_t)i * Dv] : 0.f;
-    }
     const T* qkv = (const T*)a.qkv;
     const T* proj = (const T*)a.proj;
 
-    // what a thread fetches of a chunk of tokens: its warp's tokens' q and k (lane l: dims l, l + 32, ...),
-    // their b and a, and the values (token tid / 32 + 4 m, column tid % 32)
-    float kpre[TPW][DC], qpre[TPW][DC], bpre[TPW], apre[TPW], vpre[TPW];
-    auto fetch = [&](int tc) {
+    // ---- staging warps: tokens tc + sw, tc + sw + 4, ... of a chunk become unit q and k, beta, the decay
+    // and the block's columns of v in buffer `buf`
+    auto stage = [&](int tc, int buf) {
+        const int sw = warp - WALKERS / 32;
 #pragma unroll
         for (int m = 0; m < TPW; ++m) {
-            const int t = tc + warp + 4 * m;
-            const bool have = t < t1;
-            const T* xr = qkv + (size_t)(have ? t : t0) * a.qkv_stride;
-            const T* pr = proj + (size_t)(have ? t : t0) * a.proj_stride;
+            const int tt = sw + (STAGERS / 32) * m, t = tc + tt;
+            if (t >= t1) break;
+            const T* xr = qkv + (size_t)t * a.qkv_stride;
+            const T* pr = proj + (size_t)t * a.proj_stride;
+            float kv[DC], qv[DC], kss = 0.f, qss = 0.f;
 #pragma unroll
             for (int c = 0; c < DC; ++c) {
                 const int d = c * 32 + lane;
-                kpre[m][c] = (have && d < D) ? to_float(xr[a.k_off + kh * D + d]) : 0.f;
-                qpre[m][c] = (have && d < D) ? to_float(xr[a.q_off + kh * D + d]) : 0.f;
+                kv[c] = d < D ? to_float(xr[a.k_off + kh * D + d]) : 0.f;
+                qv[c] = d < D ? to_float(xr[a.q_off + kh * D + d]) : 0.f;
+                kss += kv[c] * kv[c];
+                qss += qv[c] * qv[c];
             }
-            bpre[m] = to_float(pr[a.b_off + h]);
-            apre[m] = to_float(pr[a.a_off + h]);
-            vpre[m] = (have && c0 + lane < Dv) ? to_float(xr[a.v_off + h * Dv + c0 + lane]) : 0.f;
-        }
-    };
-    fetch(t0);
-    for (int tc = t0; tc < t1; tc += TB) {
-        const int nt = min(TB, t1 - tc);
-        // ---- the fetched tokens become unit q and k, beta and the decay in shared memory
-#pragma unroll
-        for (int m = 0; m < TPW; ++m) {
-            const int tt = warp + 4 * m;
-            float kss = 0.f, qss = 0.f;
-#pragma unroll
-            for (int c = 0; c < DC; ++c) { kss += kpre[m][c] * kpre[m][c]; qss += qpre[m][c] * qpre[m][c]; }
+            const float v = c0 + lane < Dv ? to_float(xr[a.v_off + h * Dv + c0 + lane]) : 0.f;
+            const float bz = to_float(pr[a.b_off + h]), az = to_float(pr[a.a_off + h]);
             kss = warp_sum(kss);
             qss = warp_sum(qss);
             const float kinv = 1.0f / sqrtf(kss + 1e-6f), qinv = a.q_scale / sqrtf(qss + 1e-6f);
@@ -123,59 +108,82 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(DeltaArgs a) {
                 const int d = c * 32 + lane;
                 if (d < RG * DR) {
                     const int at = (d / DR) * (DR + 4) + d % DR;
-                    ks[tt][at] = kpre[m][c] * kinv;
-                    qs[tt][at] = qpre[m][c] * qinv;
+                    ks[buf][tt][at] = kv[c] * kinv;
+                    qs[buf][tt][at] = qv[c] * qinv;
                 }
             }
-            vs[tt][lane] = vpre[m];
+            vs[buf][tt][lane] = v;
             if (lane == 0) {
-                beta_s[tt] = 1.0f / (1.0f + expf(-bpre[m]));
-                decay_s[tt] = expf(neg_rate * softplus(apre[m] + dt_bias));
+                beta_s[buf][tt] = 1.0f / (1.0f + expf(-bz));
+                decay_s[buf][tt] = expf(neg_rate * softplus(az + dt_bias));
             }
         }
-        __syncthreads();
-        if (tc + TB < t1) fetch(tc + TB);            // in flight while this chunk is walked
-        // ---- the walk
-        for (int tt = 0; tt < nt; ++tt) {
-            const float4* k4 = reinterpret_cast<const float4*>(&ks[tt][rg * (DR + 4)]);
-            const float4* q4 = reinterpret_cast<const float4*>(&qs[tt][rg * (DR + 4)]);
-            const float decay = decay_s[tt], beta = beta_s[tt], v = vs[tt][cj];
-            float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;      // what the state already answers along k
+    };
+
+    const int rg = tid & (RG - 1), cj = (tid / RG) & (COLS - 1), j = c0 + cj;
+    const bool col = walker && j < Dv;
+    float* sp = a.state + ((size_t)a.seq_rows[r] * H + h) * D * Dv + j;
+    float S[DR];
+    if (walker) {
 #pragma unroll
-            for (int x = 0; x < DR / 4; ++x) {
-                const float4 k = k4[x];
-                r0 = fmaf(S[4 * x], k.x, r0); r1 = fmaf(S[4 * x + 1], k.y, r1);
-                r2 = fmaf(S[4 * x + 2], k.z, r2); r3 = fmaf(S[4 * x + 3], k.w, r3);
-            }
-            float rk = (r0 + r1) + (r2 + r3);
-            rk += __shfl_xor_sync(0xffffffffu, rk, 1);
-            rk += __shfl_xor_sync(0xffffffffu, rk, 2);
-            const float u = beta * (v - decay * rk);
-            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-#pragma unroll
-            for (int x = 0; x < DR / 4; ++x) {
-                const float4 k = k4[x], q = q4[x];
-                S[4 * x] = fmaf(k.x, u, decay * S[4 * x]);         o0 = fmaf(S[4 * x], q.x, o0);
-                S[4 * x + 1] = fmaf(k.y, u, decay * S[4 * x + 1]); o1 = fmaf(S[4 * x + 1], q.y, o1);
-                S[4 * x + 2] = fmaf(k.z, u, decay * S[4 * x + 2]); o2 = fmaf(S[4 * x + 2], q.z, o2);
-                S[4 * x + 3] = fmaf(k.w, u, decay * S[4 * x + 3]); o3 = fmaf(S[4 * x + 3], q.w, o3);
-            }
-            float o = (o0 + o1) + (o2 + o3);
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            if (rg == 0) os[tt][cj] = o;
+        for (int ii = 0; ii < DR; ++ii) {
+            const int i = rg * DR + ii;
+            S[ii] = (col && i < D) ? sp[(size_t)i * Dv] : 0.f;
         }
-        __syncthreads();
-#pragma unroll
-        for (int m = 0; m < TPW; ++m) {
-            const int tt = warp + 4 * m;
-            if (tt < nt && c0 + lane < Dv) a.raw_o[(size_t)(tc + tt) * H * Dv + h * Dv + c0 + lane] = os[tt][lane];
-        }
+    } else {
+        stage(t0, 0);
     }
+    __syncthreads();
+    int buf = 0;
+    for (int tc = t0; tc < t1; tc += TB, buf ^= 1) {
+        const int nt = min(TB, t1 - tc);
+        if (!walker) {
+            if (tc + TB < t1) stage(tc + TB, buf ^ 1);        // while the walkers are busy with this chunk
+        } else {
+            for (int tt = 0; tt < nt; ++tt) {
+                const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][tt][rg * (DR + 4)]);
+                const float4* q4 = reinterpret_cast<const float4*>(&qs[buf][tt][rg * (DR + 4)]);
+                const float decay = decay_s[buf][tt], beta = beta_s[buf][tt], v = vs[buf][tt][cj];
+                float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;      // what the state already answers along k
+                float4 kk[DR / 4];
 #pragma unroll
-    for (int ii = 0; ii < DR; ++ii) {
-        const int i = rg * DR + ii;
-        if (col && i < D) sp[(size_t)i * Dv] = S[ii];
+                for (int x = 0; x < DR / 4; ++x) kk[x] = k4[x];
+#pragma unroll
+                for (int x = 0; x < DR / 4; ++x) {
+                    const float4 k = kk[x];
+                    r0 = fmaf(S[4 * x], k.x, r0); r1 = fmaf(S[4 * x + 1], k.y, r1);
+                    r2 = fmaf(S[4 * x + 2], k.z, r2); r3 = fmaf(S[4 * x + 3], k.w, r3);
+                }
+                float rk = (r0 + r1) + (r2 + r3);
+                rk += __shfl_xor_sync(0xffffffffu, rk, 1);
+                rk += __shfl_xor_sync(0xffffffffu, rk, 2);
+                const float u = beta * (v - decay * rk);
+                float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+                for (int x = 0; x < DR / 4; ++x) {
+                    const float4 k = kk[x], q = q4[x];
+                    S[4 * x] = fmaf(k.x, u, decay * S[4 * x]);         o0 = fmaf(S[4 * x], q.x, o0);
+                    S[4 * x + 1] = fmaf(k.y, u, decay * S[4 * x + 1]); o1 = fmaf(S[4 * x + 1], q.y, o1);
+                    S[4 * x + 2] = fmaf(k.z, u, decay * S[4 * x + 2]); o2 = fmaf(S[4 * x + 2], q.z, o2);
+                    S[4 * x + 3] = fmaf(k.w, u, decay * S[4 * x + 3]); o3 = fmaf(S[4 * x + 3], q.w, o3);
+                }
+                float o = (o0 + o1) + (o2 + o3);
+                o += __shfl_xor_sync(0xffffffffu, o, 1);
+                o += __shfl_xor_sync(0xffffffffu, o, 2);
+                if (rg == 0) os[tt][cj] = o;
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(WALKERS) : "memory");      // the walkers only
+            for (int tt = warp; tt < nt; tt += WALKERS / 32)
+                if (c0 + lane < Dv) a.raw_o[(size_t)(tc + tt) * H * Dv + h * Dv + c0 + lane] = os[tt][lane];
+        }
+        __syncthreads();
+    }
+    if (walker) {
+#pragma unroll
+        for (int ii = 0; ii < DR; ++ii) {
+            const int i = rg * DR + ii;
+            if (col && i < D) sp[(size_t)i * Dv] = S[ii];
+        }
     }
 }
 

@@ -110,29 +110,45 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
     }
 }
 
-// One block per token: the row of x goes to shared memory once (as float32), then every warp takes
-// every fourth router output and sums over K in a fixed order, whatever the batch holds.
+// A block per (token, four router outputs): the row of x goes to shared memory once (as float32), then each
+// warp sums one output over K in a fixed order, whatever the batch holds: lane l takes elements l, l + 32,
+// ..., eight loads in flight, four partial sums joined in a fixed tree.
 template <typename T>
 __global__ void __launch_bounds__(128) moe_logits_kernel(float* __restrict__ logits, const T* __restrict__ x,
                                                          const float* __restrict__ router, int E, int K) {
     sb::pdl_launch_dependents();
     extern __shared__ float xs[];
     const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.y * 4 + warp;
+    const float* w = router + (size_t)(e < E ? e : 0) * K;
+    float wv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wv[j] = lane + 32 * j < K ? w[lane + 32 * j] : 0.f;     // weights: before the wait
     sb::pdl_wait();
     for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float(x[(size_t)n * K + k]);
     __syncthreads();
-    for (int e = warp; e < E; e += 4) {
-        const float* w = router + (size_t)e * K;
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        int k = lane;
-        for (; k + 96 < K; k += 128) {
-            a0 = fmaf(xs[k], w[k], a0); a1 = fmaf(xs[k + 32], w[k + 32], a1);
-            a2 = fmaf(xs[k + 64], w[k + 64], a2); a3 = fmaf(xs[k + 96], w[k + 96], a3);
+    if (e >= E) return;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    for (int k0 = 0; k0 < K; k0 += 256) {
+        float nx[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {                       // the next eight are on their way while these are used
+            const int k = k0 + 256 + lane + 32 * j;
+            nx[j] = k < K ? w[k] : 0.f;
         }
-        for (; k < K; k += 32) a0 = fmaf(xs[k], w[k], a0);
-        const float total = warp_sum((a0 + a1) + (a2 + a3));
-        if (lane == 0) logits[(size_t)n * E + e] = total;
+#pragma unroll
+        for (int j = 0; j < 8; j += 4) {
+            const int k = k0 + lane + 32 * j;
+            a0 = fmaf(k < K ? xs[k] : 0.f, wv[j], a0);
+            a1 = fmaf(k + 32 < K ? xs[k + 32] : 0.f, wv[j + 1], a1);
+            a2 = fmaf(k + 64 < K ? xs[k + 64] : 0.f, wv[j + 2], a2);
+            a3 = fmaf(k + 96 < K ? xs[k + 96] : 0.f, wv[j + 3], a3);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) wv[j] = nx[j];
     }
+    const float total = warp_sum((a0 + a1) + (a2 + a3));
+    if (lane == 0) logits[(size_t)n * E + e] = total;
 }
 
 template <typename T>
@@ -211,6 +227,7 @@ extern "C" int sb_moe_logits(float* logits, const void* x, const float* router, 
     SB_REQUIRE(N >= 0 && E > 0 && K > 0, "moe_logits: bad sizes N=%d E=%d K=%d", N, E, K);
     const size_t smem = (size_t)K * sizeof(float);
     SB_REQUIRE(smem <= 160 * 1024, "moe_logits: rows of %d values do not fit a block's shared memory", K);
+    SB_REQUIRE((E + 3) / 4 <= 65535 && N <= 2147483647, "moe_logits: too many router outputs");
     if (N == 0) return 0;
     static sb::OncePerDevice once_f, once_b;
     if (dtype == SB_F32) {
@@ -218,13 +235,13 @@ extern "C" int sb_moe_logits(float* logits, const void* x, const float* router, 
             cudaFuncSetAttribute(moe_logits_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
             once_f.flag() = true;
         }
-        sb::launch(moe_logits_kernel<float>, dim3(N), dim3(128), smem, stream, logits, (const float*)x, router, E, K);
+        sb::launch(moe_logits_kernel<float>, dim3(N, (E + 3) / 4), dim3(128), smem, stream, logits, (const float*)x, router, E, K);
     } else if (dtype == SB_BF16) {
         if (smem > 48 * 1024 && !once_b.flag()) {
             cudaFuncSetAttribute(moe_logits_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
             once_b.flag() = true;
         }
-        sb::launch(moe_logits_kernel<__nv_bfloat16>, dim3(N), dim3(128), smem, stream, logits, (const __nv_bfloat16*)x,
+        sb::launch(moe_logits_kernel<__nv_bfloat16>, dim3(N, (E + 3) / 4), dim3(128), smem, stream, logits, (const __nv_bfloat16*)x,
                    router, E, K);
     } else {
         SB_REQUIRE(false, "moe_logits: unknown dtype %d", dtype);
