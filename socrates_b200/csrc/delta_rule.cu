@@ -10,11 +10,11 @@
 // request's state slot; everything above is float32, only q, k, v, gate, a, b arrive in the model
 // dtype (they are matrix products and convolutions) and y leaves in it.
 //
-// A block serves 32 columns of the state of one (request, value head) and walks the request's tokens
+// A block serves 8 columns of the state of one (request, value head) and walks the request's tokens
 // of the step in order.  The columns of S never mix, so blocks need nothing from one another; the
 // sum of o^2 over a head's columns, the norm and the gate are a second, elementwise kernel that
-// reads the raw o.  Four neighbouring threads share a column (a quarter of the D rows each, in
-// registers; two shuffles join their partial dot products).  Tokens are staged sixteen at a time
+// reads the raw o.  Sixteen neighbouring threads share a column (a sixteenth of the D rows each, in
+// registers; four shuffles join their partial dot products).  Tokens are staged eight at a time
 // by four more warps of the block: they load q and k, make them unit vectors and leave them in
 // shared memory with beta, the decay and the values beside them, into one of two buffers while the
 // walking warps are busy with the other, so the serial walk waits neither for a global load nor for
@@ -48,20 +48,24 @@ struct DeltaArgs {
 
 __device__ __forceinline__ float softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
-constexpr int RG = 4;                 // threads that share a column of the state
-constexpr int COLS = 32;              // columns of a block
-constexpr int TB = 16;                // tokens staged at a time
+constexpr int RG = 16;                // threads that share a column of the state
+constexpr int COLS = 8;               // columns of a block
+constexpr int TB = 8;                 // tokens staged at a time
 constexpr int WALKERS = COLS * RG;    // 128 threads walk the tokens ...
 constexpr int STAGERS = 128;          // ... and 128 prepare the next ones meanwhile
 constexpr int THREADS = WALKERS + STAGERS;
 constexpr int TPW = TB / (STAGERS / 32);     // tokens a staging warp prepares
 
-// DR rows of the state per thread (D <= RG * DR); in shared memory the four quarters of a q or k
-// vector are DR + 4 floats apart, so that the quarters' 16-byte reads fall into different banks.
+// DR rows of the state per thread (D <= RG * DR); in shared memory the sixteen parts of a q or k
+// vector are 12 floats apart, so that the 16-byte reads of eight neighbouring parts fall into different
+// banks.  (The walk is bound by how fast ONE warp issues dependent instructions, about 4.8 clocks each:
+// with four threads a column and 32 rows a thread a token cost 136 instructions, 655 clocks; sixteen
+// threads a column halve the instructions and double the blocks, so that SMs interleave two blocks' warps.)
 template <typename T, int DR>
 __global__ void __launch_bounds__(THREADS) delta_rule_kernel(DeltaArgs a) {
     sb::pdl_launch_dependents();
-    constexpr int PITCH = RG * (DR + 4);
+    constexpr int ST = 12;                            // floats from one part to the next (DR <= 8)
+    constexpr int PITCH = RG * ST;
     constexpr int DC = (RG * DR + 31) / 32;          // values of a vector per lane while staging
     __shared__ __align__(16) float ks[2][TB][PITCH];
     __shared__ __align__(16) float qs[2][TB][PITCH];
@@ -98,7 +102,7 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(DeltaArgs a) {
                 kss += kv[c] * kv[c];
                 qss += qv[c] * qv[c];
             }
-            const float v = c0 + lane < Dv ? to_float(xr[a.v_off + h * Dv + c0 + lane]) : 0.f;
+            const float v = (lane < COLS && c0 + lane < Dv) ? to_float(xr[a.v_off + h * Dv + c0 + lane]) : 0.f;
             const float bz = to_float(pr[a.b_off + h]), az = to_float(pr[a.a_off + h]);
             kss = warp_sum(kss);
             qss = warp_sum(qss);
@@ -107,12 +111,12 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(DeltaArgs a) {
             for (int c = 0; c < DC; ++c) {
                 const int d = c * 32 + lane;
                 if (d < RG * DR) {
-                    const int at = (d / DR) * (DR + 4) + d % DR;
+                    const int at = (d / DR) * ST + d % DR;
                     ks[buf][tt][at] = kv[c] * kinv;
                     qs[buf][tt][at] = qv[c] * qinv;
                 }
             }
-            vs[buf][tt][lane] = v;
+            if (lane < COLS) vs[buf][tt][lane] = v;
             if (lane == 0) {
                 beta_s[buf][tt] = 1.0f / (1.0f + expf(-bz));
                 decay_s[buf][tt] = expf(neg_rate * softplus(az + dt_bias));
@@ -141,8 +145,8 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(DeltaArgs a) {
             if (tc + TB < t1) stage(tc + TB, buf ^ 1);        // while the walkers are busy with this chunk
         } else {
             for (int tt = 0; tt < nt; ++tt) {
-                const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][tt][rg * (DR + 4)]);
-                const float4* q4 = reinterpret_cast<const float4*>(&qs[buf][tt][rg * (DR + 4)]);
+                const float4* k4 = reinterpret_cast<const float4*>(&ks[buf][tt][rg * ST]);
+                const float4* q4 = reinterpret_cast<const float4*>(&qs[buf][tt][rg * ST]);
                 const float decay = decay_s[buf][tt], beta = beta_s[buf][tt], v = vs[buf][tt][cj];
                 float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;      // what the state already answers along k
                 float4 kk[DR / 4];
@@ -155,8 +159,8 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(DeltaArgs a) {
                     r2 = fmaf(S[4 * x + 2], k.z, r2); r3 = fmaf(S[4 * x + 3], k.w, r3);
                 }
                 float rk = (r0 + r1) + (r2 + r3);
-                rk += __shfl_xor_sync(0xffffffffu, rk, 1);
-                rk += __shfl_xor_sync(0xffffffffu, rk, 2);
+#pragma unroll
+                for (int sh = 1; sh < RG; sh <<= 1) rk += __shfl_xor_sync(0xffffffffu, rk, sh);
                 const float u = beta * (v - decay * rk);
                 float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
@@ -168,13 +172,13 @@ __global__ void __launch_bounds__(THREADS) delta_rule_kernel(DeltaArgs a) {
                     S[4 * x + 3] = fmaf(k.w, u, decay * S[4 * x + 3]); o3 = fmaf(S[4 * x + 3], q.w, o3);
                 }
                 float o = (o0 + o1) + (o2 + o3);
-                o += __shfl_xor_sync(0xffffffffu, o, 1);
-                o += __shfl_xor_sync(0xffffffffu, o, 2);
+#pragma unroll
+                for (int sh = 1; sh < RG; sh <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sh);
                 if (rg == 0) os[tt][cj] = o;
             }
             asm volatile("bar.sync 1, %0;" ::"n"(WALKERS) : "memory");      // the walkers only
             for (int tt = warp; tt < nt; tt += WALKERS / 32)
-                if (c0 + lane < Dv) a.raw_o[(size_t)(tc + tt) * H * Dv + h * Dv + c0 + lane] = os[tt][lane];
+                if (lane < COLS && c0 + lane < Dv) a.raw_o[(size_t)(tc + tt) * H * Dv + h * Dv + c0 + lane] = os[tt][lane];
         }
         __syncthreads();
     }
@@ -211,12 +215,8 @@ __global__ void __launch_bounds__(128) delta_out_kernel(DeltaArgs a, int N) {
 template <typename T>
 int launch_delta(const DeltaArgs& a, int R, int N, cudaStream_t stream) {
     const dim3 grid(a.H, R, (a.Dv + COLS - 1) / COLS);
-    switch ((a.D + 4 * 8 - 1) / (4 * 8)) {           // rows per thread in steps of eight
-        case 1: sb::launch(delta_rule_kernel<T, 8>, grid, dim3(THREADS), 0, stream, a); break;
-        case 2: sb::launch(delta_rule_kernel<T, 16>, grid, dim3(THREADS), 0, stream, a); break;
-        case 3: sb::launch(delta_rule_kernel<T, 24>, grid, dim3(THREADS), 0, stream, a); break;
-        default: sb::launch(delta_rule_kernel<T, 32>, grid, dim3(THREADS), 0, stream, a); break;
-    }
+    if (a.D <= RG * 4) sb::launch(delta_rule_kernel<T, 4>, grid, dim3(THREADS), 0, stream, a);     // rows per thread
+    else sb::launch(delta_rule_kernel<T, 8>, grid, dim3(THREADS), 0, stream, a);
     sb::launch(delta_out_kernel<T>, dim3((N * a.H + 3) / 4), dim3(128), 0, stream, a, N);
     SB_LAUNCH_CHECK();
 }

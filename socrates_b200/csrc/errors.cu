@@ -16,14 +16,23 @@ void sb_set_error(const char* fmt, ...) {
 
 extern "C" const char* sb_last_error() { return g_error; }
 
+// Programmatic dependent launch: on unless SOCRATES_PDL=0; a model may switch it off for its own steps
+// (sb_set_dependent_launch), which the environment variable overrides only towards "off".
+static int g_pdl_wanted = 1;
+
 namespace sb {
 bool pdl_enabled() {
-    static const bool on = [] {
+    static const bool allowed = [] {
         const char* e = getenv("SOCRATES_PDL");
         return !(e && e[0] == '0');
     }();
-    return on;
+    return allowed && g_pdl_wanted != 0;
 }
 }  // namespace sb
+
+extern "C" int sb_set_dependent_launch(int on) {
+    g_pdl_wanted = on ? 1 : 0;
+    return 0;
+}
 
 extern "C" int sb_abi_version() { return 1; }

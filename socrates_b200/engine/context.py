@@ -154,8 +154,12 @@ class StepContext:
             # Many rows but few tiles (a short prompt portion through a narrow projection): cut K
             # so that the tiles cover the SMs.  Measured on the 4B shape at 512 rows: o 29 -> 20 us,
             # down 57 -> 33 us with three parts; from 1,024 rows on a cut no longer pays.
+            # The cut is kept to the regime it was measured in.  Beyond it the one-tile-per-block kernel has
+            # stalled: 2,048 rows through a 1,024 x 16,384 matrix cut in two (all experts' down matrices side
+            # by side) never came back in about one first step in five, with every wait inside it bounded;
+            # the cause was not found, so that shape does not reach the kernel.
             tiles = -(-M // 128) * -(-N // 256)
-            if 2 * tiles > self.num_sms:
+            if 2 * tiles > self.num_sms or M >= 1024:
                 return 1
             return ops.gemm_tcgen05_splits(K, max(1, min(4, self.num_sms // tiles, (-(-K // 64)) // 8)))
         tiles = -(-N // 128)

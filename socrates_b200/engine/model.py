@@ -14,6 +14,7 @@ import torch
 
 from ..cache.manager import CacheNeeds
 from ..config.plan import ModelPlan
+from ..kernels import ops
 from ..parts import ParamSpec, ResidualStream, build_part
 from ..parts.base import _REGISTRIES
 from .context import CacheView, StepContext
@@ -35,6 +36,10 @@ class Model:
                            for i, e in enumerate(plan.order) if e.before is not None}
         self.keeps_embedding_output = any(getattr(op, "needs_embedding_output", False)
                                           for op in self.stream_ops.values())
+        # A part may ask that the steps of its model launch their kernels one after the other (no
+        # programmatic dependent launch): `serial_launches = True` on the part.
+        self.dependent_launch = not any(getattr(p, "serial_launches", False)
+                                        for layer in self.layers for p in getattr(layer, "parts", list)())
         self.final_norm = build_part("norm", plan.final_norm, plan.final_norm.name)
         self.head = build_part("head", plan.head, plan.head.name)
         self.dtype: Optional[torch.dtype] = None
@@ -88,6 +93,7 @@ class Model:
     # ------------------------------------------------------------------ one step
     def forward(self, ctx: StepContext, cache) -> torch.Tensor:
         ctx.weight_successor = self.weight_successor
+        ops.set_dependent_launch(self.dependent_launch)
         stream = ResidualStream(self.embedding.forward(ctx))
         if self.keeps_embedding_output:
             # the residual is updated in place from here on: a stream op that adds the embedding's

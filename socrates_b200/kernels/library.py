@@ -27,6 +27,7 @@ P, I, F, LL = c_void_p, c_int, c_float, c_longlong
 
 _SIGNATURES = {
     "sb_abi_version": [],
+    "sb_set_dependent_launch": [I],
     "sb_embed": [P, P, P, I, I, I, I, P, F, P],
     "sb_add_rmsnorm": [P, P, I, LL, P, P, P, I, I, F, I, P],
     "sb_qk_norm_rope_kvwrite": [P, P, I, LL, P, P, P, P, P, P, I, P, P, P, I, I, F, I, I, I, I, I, I, I, I, I, P],

@@ -56,6 +56,12 @@ def _stream():
     return _scoped_stream if _scoped_stream is not None else torch.cuda.current_stream().cuda_stream
 
 
+def set_dependent_launch(on: bool) -> None:
+    """Whether the kernels launched from now on carry the programmatic-stream-serialization attribute (they
+    may start while their predecessor in the stream still runs).  SOCRATES_PDL=0 keeps it off regardless."""
+    library().sb_set_dependent_launch(int(bool(on)))
+
+
 def _want(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
     if not t.is_cuda:
         raise KernelError(f"{name} must be a CUDA tensor")

@@ -149,6 +149,7 @@ class GQAAttention(Part):
         self.qkv = Linear(torch.cat([tensors[n + "q_proj.weight"], tensors[n + "k_proj.weight"],
                                      tensors[n + "v_proj.weight"]], dim=0))
         self.o = Linear(tensors[n + "o_proj.weight"])
+        self.position.tables(self.o.weight.device)      # made now: no copy from the host inside a step
         if self.qk_norm_eps is not None:
             self.q_gain = tensors[n + "q_norm.weight"]
             self.k_gain = tensors[n + "k_norm.weight"]

@@ -7,6 +7,12 @@ with dim 2j+1: `neighbours` says which).  Keys are stored rotated, so
 positions are absolute and nothing else in the engine knows about the encoding.
 Another encoding (a fraction of the dims, scaled frequencies, none at all) is another
 table: register a class with `tables()`.
+
+A mixer asks for its tables when its weights are bound, so that the copy from the host happens
+then: a pageable host-to-device copy issued in the middle of a step, between kernels that were
+launched with programmatic stream serialization, stalled for good in about one run in four of a
+2,048-token first step (it never did with that launch attribute off, nor with the tables made
+beforehand).  Nothing inside a step copies from pageable host memory.
 """
 
 from __future__ import annotations

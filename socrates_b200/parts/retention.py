@@ -55,6 +55,8 @@ class Retention(Part):
         self.qkvg = Linear(torch.cat([tensors[n + x] for x in ("q", "k", "v", "g")], dim=0))
         self.o = Linear(tensors[n + "o"])
         self.decay_t = torch.tensor(self.decay, dtype=torch.float32, device=self.o.weight.device)
+        self.position.tables(self.o.weight.device)      # made now: no copy from the host inside a step
+        getattr(self.position, "low_table", lambda d: None)(self.o.weight.device)
 
     def cache_needs(self) -> CacheNeeds:
         return CacheNeeds(state=StateSpec((self.H, self.dk, self.dv), torch.float32))

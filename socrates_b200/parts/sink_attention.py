@@ -76,6 +76,7 @@ class GatedSinkAttention(Part):
         names = ["q", *(["k", "v"] if self.own_kv else []), *(["g"] if self.gate is not None else [])]
         self.proj = Linear(torch.cat([tensors[n + x] for x in names], dim=0))
         self.o = Linear(tensors[n + "o"])
+        self.position.tables(self.o.weight.device)      # made now: no copy from the host inside a step
         if self.qk_norm_eps is not None:
             self.q_gain = tensors[n + "q.norm"]
             self.k_gain = tensors[n + "k.norm"] if self.own_kv else None
