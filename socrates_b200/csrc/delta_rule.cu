@@ -64,7 +64,7 @@ constexpr int TPW = TB / (STAGERS / 32);     // tokens a staging warp prepares
 template <typename T, int DR>
 __global__ void __launch_bounds__(THREADS) delta_rule_kernel(DeltaArgs a) {
     sb::pdl_launch_dependents();
-    constexpr int ST = 12;                            // floats from one part to the next (DR <= 8)
+    constexpr int ST = DR <= 8 ? 12 : DR + 4;         // floats from one part to the next: an odd number of 16-byte pieces
     constexpr int PITCH = RG * ST;
     constexpr int DC = (RG * DR + 31) / 32;          // values of a vector per lane while staging
     __shared__ __align__(16) float ks[2][TB][PITCH];
@@ -216,7 +216,8 @@ template <typename T>
 int launch_delta(const DeltaArgs& a, int R, int N, cudaStream_t stream) {
     const dim3 grid(a.H, R, (a.Dv + COLS - 1) / COLS);
     if (a.D <= RG * 4) sb::launch(delta_rule_kernel<T, 4>, grid, dim3(THREADS), 0, stream, a);     // rows per thread
-    else sb::launch(delta_rule_kernel<T, 8>, grid, dim3(THREADS), 0, stream, a);
+    else if (a.D <= RG * 8) sb::launch(delta_rule_kernel<T, 8>, grid, dim3(THREADS), 0, stream, a);
+    else sb::launch(delta_rule_kernel<T, 16>, grid, dim3(THREADS), 0, stream, a);
     sb::launch(delta_out_kernel<T>, dim3((N * a.H + 3) / 4), dim3(128), 0, stream, a, N);
     SB_LAUNCH_CHECK();
 }
@@ -224,7 +225,7 @@ int launch_delta(const DeltaArgs& a, int R, int N, cudaStream_t stream) {
 }  // namespace
 
 // Largest key and value head sizes the kernel takes.
-extern "C" int sb_delta_rule_supports(int D, int Dv) { return D >= 1 && D <= 128 && Dv >= 1 && Dv <= 256; }
+extern "C" int sb_delta_rule_supports(int D, int Dv) { return D >= 1 && D <= 256 && Dv >= 1 && Dv <= 1024; }
 
 extern "C" int sb_delta_rule(void* out, const void* qkv, long long qkv_stride, int q_off, int k_off, int v_off,
                              const void* proj, long long proj_stride, int gate_off, int b_off, int a_off,
@@ -232,8 +233,8 @@ extern "C" int sb_delta_rule(void* out, const void* qkv, long long qkv_stride, i
                              const int* seq_starts, const int* seq_rows, int R, int H, int G, int D, int Dv,
                              float eps, float q_scale, int dtype, float* raw_o, int N, cudaStream_t stream) {
     SB_REQUIRE(R >= 0 && H > 0 && G > 0 && H % G == 0, "delta_rule: %d value heads are no multiple of %d key heads", H, G);
-    SB_REQUIRE(sb_delta_rule_supports(D, Dv), "delta_rule: heads of %d (keys, at most 128) and %d (values, at most 256) dims", D, Dv);
-    SB_REQUIRE(R <= 65535, "delta_rule: %d requests exceed one launch", R);
+    SB_REQUIRE(sb_delta_rule_supports(D, Dv), "delta_rule: heads of %d (keys, at most 256) and %d (values, at most 1024) dims", D, Dv);
+    SB_REQUIRE(R <= 65535 && (Dv + COLS - 1) / COLS <= 65535, "delta_rule: %d requests exceed one launch", R);
     SB_REQUIRE(raw_o != nullptr && N >= 0, "delta_rule: scratch for %d tokens is missing", N);
     if (R == 0 || N == 0) return 0;
     DeltaArgs a;

@@ -830,7 +830,7 @@ def attention_bias_tile(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor
 # Gated delta rule and the routing of a mixture of experts.
 
 def delta_rule_supports(key_dim: int, value_dim: int) -> bool:
-    """Whether the delta-rule kernel takes heads of these sizes (keys up to 128 dims, values up to 256)."""
+    """Whether the delta-rule kernel takes heads of these sizes (keys up to 256 dims, values up to 1,024)."""
     return bool(library().sb_delta_rule_supports(int(key_dim), int(value_dim)))
 
 

@@ -45,8 +45,8 @@ class GatedDeltaRule(Part):
             raise ValueError(f"{self.H} value heads are no multiple of {self.G} key heads")
         if not 1 <= self.taps <= 16:
             raise ValueError(f"{self.taps} convolution taps; the kernel takes 1 to 16")
-        if not (1 <= self.dk <= 128 and 1 <= self.dv <= 256):
-            raise ValueError(f"head sizes {self.dk} (keys, at most 128) and {self.dv} (values, at most 256)")
+        if not (1 <= self.dk <= 256 and 1 <= self.dv <= 1024):
+            raise ValueError(f"head sizes {self.dk} (keys, at most 256) and {self.dv} (values, at most 1024)")
         self.Cqk, self.Cv = self.G * self.dk, self.H * self.dv
         self.C = 2 * self.Cqk + self.Cv                      # channels that pass the convolution
         self.proj: Optional[Linear] = None

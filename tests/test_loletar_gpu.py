@@ -211,7 +211,8 @@ def test_tensor_core_attention_with_a_sink_and_a_gate(shape):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("shape", [(4, 2, 16, 8), (1, 1, 40, 40), (2, 1, 8, 72), (3, 3, 128, 32), (2, 2, 33, 200)])
+@pytest.mark.parametrize("shape", [(4, 2, 16, 8), (1, 1, 40, 40), (2, 1, 8, 72), (3, 3, 128, 32), (2, 2, 33, 200), (2, 1, 160, 24),
+                                   (1, 1, 256, 300)])
 def test_delta_rule_kernel_in_portions(dtype, shape):
     """Three sequences of unequal length share the steps, cut at different places down to one token; the
     states live in slots that a previous owner left dirty and `assign` cleared."""
@@ -264,12 +265,12 @@ def test_delta_rule_kernel_in_portions(dtype, shape):
 
 def test_delta_rule_refuses_heads_it_cannot_hold():
     from socrates_b200.kernels import KernelError, ops
-    assert ops.delta_rule_supports(128, 256) and not ops.delta_rule_supports(129, 8) and not ops.delta_rule_supports(8, 257)
-    z = torch.zeros(1, 2 * 136 + 8, device=DEV)
+    assert ops.delta_rule_supports(256, 1024) and not ops.delta_rule_supports(257, 8) and not ops.delta_rule_supports(8, 1025)
+    z = torch.zeros(1, 2 * 264 + 8, device=DEV)
     with pytest.raises(KernelError):
-        ops.delta_rule(torch.zeros(1, 8, device=DEV), z, (0, 136, 272), torch.zeros(1, 10, device=DEV), (0, 8, 9),
+        ops.delta_rule(torch.zeros(1, 8, device=DEV), z, (0, 264, 528), torch.zeros(1, 10, device=DEV), (0, 8, 9),
                        torch.zeros(1, device=DEV), torch.zeros(1, device=DEV), torch.ones(8, device=DEV),
-                       torch.zeros(1, 1, 136, 8, device=DEV), i32([0, 1]), i32([0]), 1, 1, 136, 8, 1e-5, 1.0)
+                       torch.zeros(1, 1, 264, 8, device=DEV), i32([0, 1]), i32([0]), 1, 1, 264, 8, 1e-5, 1.0)
 
 
 @pytest.mark.parametrize("case", [(11, 4, 5, 3, 4), (6, 0, 1, 1, 1), (5, 1, 3, 2, 2), (3, 3, 2, 1, 2), (40, 8, 6, 6, 5), (7, 0, 7, 3, 3)])
