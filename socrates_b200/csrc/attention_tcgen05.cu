@@ -544,7 +544,16 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_k, const __g
                     tmem_ld_wait();
                     if (tok < n_tok) {
                         float* fo = reinterpret_cast<float*>(ov);
-                        if (gate && gate_per_dim) {
+                        if (gate && gate_per_dim == 2) {            // rows of the gate are 16-byte aligned
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint4 gv = *reinterpret_cast<const uint4*>(grow_ptr + c + 8 * j);
+                                const bf16* gb = reinterpret_cast<const bf16*>(&gv);
+#pragma unroll
+                                for (int x = 0; x < 8; ++x)
+                                    fo[8 * j + x] *= 1.0f / (1.0f + expf(-__bfloat162float(gb[x])));
+                            }
+                        } else if (gate && gate_per_dim) {
 #pragma unroll
                             for (int x = 0; x < 32; ++x)
                                 fo[x] *= 1.0f / (1.0f + expf(-__bfloat162float(grow_ptr[c + x])));
@@ -622,6 +631,8 @@ extern "C" int sb_attention_prefill_tcgen05(void* out, const void* q, const void
                                             const void* gate, long long gate_stride, int gate_per_dim, int has_sink,
                                             float sink, cudaStream_t stream) {
     SB_REQUIRE(!has_sink || scale > 0.f, "attention_tcgen05: a sink needs a positive scale");
+    if (gate != nullptr && gate_per_dim && (reinterpret_cast<uintptr_t>(gate) & 15) == 0 && gate_stride % 8 == 0)
+        gate_per_dim = 2;                                  // 16-byte loads of the gate
     SB_REQUIRE(sb_attention_tcgen05_supports(Hq, Hkv, D, page_size),
                "attention_tcgen05: Hq=%d Hkv=%d head_dim=%d page_size=%d is not supported", Hq, Hkv, D, page_size);
     SB_REQUIRE(R > 0 && N > 0 && window >= 0 && table_width > 0 && table_width <= 4096 && num_pages > 0,
